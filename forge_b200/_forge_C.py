@@ -1,0 +1,101 @@
+"""Python-level mirror of the reference's `forge._forge_C` extension functions for the
+quantized-inference path (reference python/forge/csrc/bindings.cpp:446-575): same names,
+argument lists and return values, taking torch CUDA tensors and running on torch's current
+stream. Each function forwards to the C ABI of libforge_b200.so through ctypes.
+"""
+import torch
+
+from . import _lib
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def fused_quantize_activation(input, M, K):
+    """bindings.cpp:448-459 -> (int8 (M,K), float32 (M,))."""
+    output = torch.empty((M, K), dtype=torch.int8, device=input.device)
+    scales = torch.empty((M,), dtype=torch.float32, device=input.device)
+    _lib.call("forge_fused_quantize_activation", _ptr(input), _ptr(output), _ptr(scales), M, K, _stream())
+    return output, scales
+
+
+def fused_dequantize_bias(input, act_scale, w_scale, bias, M, N):
+    """bindings.cpp:461-476 -> float16 (M,N)."""
+    output = torch.empty((M, N), dtype=torch.float16, device=act_scale.device)
+    _lib.call("forge_fused_dequantize_bias", _ptr(input), _ptr(act_scale), _ptr(w_scale), _ptr(bias), _ptr(output),
+              M, N, _stream())
+    return output
+
+
+def int8_linear(x, w_int8, w_scale, bias, scratch_a_int8, scratch_a_scale):
+    """bindings.cpp:498-519 -> float16 (M,N)."""
+    M, K, N = x.size(0), x.size(1), w_int8.size(0)
+    output = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    _lib.call("forge_int8_linear", _ptr(x), _ptr(w_int8), _ptr(w_scale), _ptr(bias), _ptr(output), M, K, N,
+              _ptr(scratch_a_int8), _ptr(scratch_a_scale), _stream())
+    return output
+
+
+def sparse_int8_linear(x, W_comp, w_meta, w_scale, bias, scratch_x_int8, scratch_x_scale, splitk_workspace=None,
+                       split_k=1):
+    """bindings.cpp:521-554 -> float16 (M,N_out). The workspace is accepted for compatibility;
+    this implementation never splits K, so none is allocated."""
+    M, K, N_out = x.size(0), x.size(1), W_comp.size(0)
+    output = torch.empty((M, N_out), dtype=x.dtype, device=x.device)
+    _lib.call("forge_sparse_int8_linear", _ptr(x), _ptr(W_comp), _ptr(w_meta), _ptr(w_scale), _ptr(bias),
+              _ptr(output), M, K, N_out, _ptr(scratch_x_int8), _ptr(scratch_x_scale), _ptr(splitk_workspace),
+              split_k, _stream(), -1)
+    return output
+
+
+def prune_compress_24(weight, compressed, metadata_raw, N, K):
+    """bindings.cpp:558-566."""
+    _lib.call("forge_prune_compress_24", _ptr(weight), _ptr(compressed), _ptr(metadata_raw), N, K, _stream())
+
+
+def pack_metadata(meta_raw, meta_packed, N, K):
+    """bindings.cpp:568-575."""
+    _lib.call("forge_pack_metadata", _ptr(meta_raw), _ptr(meta_packed), N, K, _stream())
+
+
+# ---- additive entry points (no counterpart in the reference extension) ----
+
+def int8_gemm_dequant(A, B, act_scale, w_scale, bias=None):
+    M, K, N = A.size(0), A.size(1), B.size(0)
+    output = torch.empty((M, N), dtype=torch.float16, device=A.device)
+    _lib.call("forge_int8_gemm_dequant", _ptr(A), _ptr(B), _ptr(act_scale), _ptr(w_scale), _ptr(bias), _ptr(output),
+              M, K, N, _stream())
+    return output
+
+
+def int8_gemm_s32(A, B):
+    M, K, N = A.size(0), A.size(1), B.size(0)
+    output = torch.empty((M, N), dtype=torch.int32, device=A.device)
+    _lib.call("forge_int8_gemm_s32", _ptr(A), _ptr(B), _ptr(output), M, K, N, _stream())
+    return output
+
+
+def sparse_int8_gemm(W_comp, x_int8, w_meta, act_scale, w_scale, bias=None, tile=-1):
+    M, K, N_out = x_int8.size(0), x_int8.size(1), W_comp.size(0)
+    output = torch.empty((M, N_out), dtype=torch.float16, device=x_int8.device)
+    _lib.call("forge_sparse_int8_gemm", _ptr(W_comp), _ptr(x_int8), _ptr(w_meta), _ptr(act_scale), _ptr(w_scale),
+              _ptr(bias), _ptr(output), M, K, N_out, 0, 1, _stream(), tile)
+    return output
+
+
+def sparse_int8_gemm_s32(W_comp, x_int8, w_meta):
+    M, K, N_out = x_int8.size(0), x_int8.size(1), W_comp.size(0)
+    output = torch.empty((M, N_out), dtype=torch.int32, device=x_int8.device)
+    _lib.call("forge_sparse_int8_gemm_s32", _ptr(W_comp), _ptr(x_int8), _ptr(w_meta), _ptr(output), M, K, N_out,
+              _stream())
+    return output
+
+
+def device_status(reset=True):
+    """Status word of the current device: 0 unless a kernel gave up on a bounded wait."""
+    return _lib.load().forge_b200_device_status(1 if reset else 0)

@@ -1,0 +1,192 @@
+// extern "C" boundary of libforge_b200.so: one symbol per reference entry point
+// (declared and cited in include/forge_b200.h). Thin argument adaptation only.
+#include "../../include/forge_b200.h"
+#include "common.cuh"
+#include "gemm_dense.cuh"
+#include "gemm_sparse.cuh"
+#include "kernels.cuh"
+
+using namespace fb200;
+
+namespace {
+
+int g_force_dense_bn = 0;
+int g_force_sparse_bt = 0;
+
+inline cudaStream_t S(forge_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+inline const __half* H(const void* p) { return static_cast<const __half*>(p); }
+inline __half* H(void* p) { return static_cast<__half*>(p); }
+
+// Tile id of the reference API -> token-tile width of the tcgen05 kernel. Weight tiles are
+// always 128 rows here; the reference's 256-row tile maps to the widest token tile.
+inline int tile_to_bt(int tile) {
+    switch (tile) {
+    case FORGE_SPARSE_TILE_256x128: return 128;
+    case FORGE_SPARSE_TILE_128x128: return 128;
+    case FORGE_SPARSE_TILE_128x64: return 64;
+    default: return 0;
+    }
+}
+
+// fp32 workspace + bias -> fp16, the contract of the reference's splitk_reduce_kernel
+// (src/gemm/int8_sparse.cu:99-111).
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __half* __restrict__ bias,
+                                     __half* __restrict__ out, int N_out, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float v = ws[i];
+    if (bias != nullptr) v += __half2float(bias[i % N_out]);
+    out[i] = __float2half_rn(v);
+}
+
+}  // namespace
+
+extern "C" {
+
+int forge_fused_quantize_activation(const void* input, int8_t* output, float* scales, int M, int K,
+                                    forge_stream_t stream) {
+    return quantize_activation(H(input), output, scales, M, K, S(stream));
+}
+
+int forge_fused_dequantize_bias(const int32_t* input, const float* act_scale, const void* w_scale, const void* bias,
+                                void* output, int M, int N, forge_stream_t stream) {
+    return dequantize_bias(input, act_scale, H(w_scale), H(bias), H(output), M, N, S(stream));
+}
+
+int forge_int8_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
+                            const void* bias, void* output, int M, int K, int N, forge_stream_t stream) {
+    return dense_gemm_dequant(A, B, act_scale, H(w_scale), H(bias), H(output), M, K, N, S(stream), g_force_dense_bn);
+}
+
+int forge_int8_gemm(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale, const void* bias,
+                    void* output, int M, int K, int N, forge_stream_t stream) {
+    return forge_int8_gemm_dequant(A, B, act_scale, w_scale, bias, output, M, K, N, stream);
+}
+
+int forge_int8_dp4a_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
+                                 const void* bias, void* output, int M, int K, int N, forge_stream_t stream) {
+    return forge_int8_gemm_dequant(A, B, act_scale, w_scale, bias, output, M, K, N, stream);
+}
+
+int forge_int8_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
+                      int M, int K, int N, int8_t* scratch_a_int8, float* scratch_a_scale, forge_stream_t stream) {
+    if (M <= 0 || K <= 0 || N <= 0) return kOk;
+    const int r = quantize_activation(H(x), scratch_a_int8, scratch_a_scale, M, K, S(stream));
+    if (r != kOk) return r;
+    return dense_gemm_dequant(scratch_a_int8, w_int8, scratch_a_scale, H(w_scale), H(bias), H(output), M, K, N,
+                              S(stream), g_force_dense_bn);
+}
+
+int forge_int8_dp4a_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
+                           int M, int K, int N, int8_t* scratch_a_int8, float* scratch_a_scale,
+                           forge_stream_t stream) {
+    return forge_int8_linear(x, w_int8, w_scale, bias, output, M, K, N, scratch_a_int8, scratch_a_scale, stream);
+}
+
+int forge_get_compute_capability(int device) {
+    int major = 0, minor = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess) return 0;
+    return major * 10 + minor;
+}
+
+int forge_has_wmma_int8(int device) { return forge_get_compute_capability(device) >= 80 ? 1 : 0; }
+
+int forge_int8_gemm_s32(const int8_t* A, const int8_t* B, int32_t* output, int M, int K, int N,
+                        forge_stream_t stream) {
+    return dense_gemm_s32(A, B, output, M, K, N, S(stream), g_force_dense_bn);
+}
+
+int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_workspace, int tile, int* out_tile,
+                                int* out_split_k) {
+    (void)K;
+    if (tile >= FORGE_SPARSE_NUM_TILES) tile = FORGE_SPARSE_TILE_AUTO;
+    int t = tile;
+    if (t < 0) {
+        // automatic: 128-token tiles once they give every SM work, else 64-token tiles
+        const long long w_blocks = (N_out + 127) / 128;
+        t = (M > 64 && w_blocks * ((M + 127) / 128) >= sm_count()) ? FORGE_SPARSE_TILE_128x128
+                                                                    : FORGE_SPARSE_TILE_128x64;
+    }
+    // The K loop is never split: the exact s32 accumulation in TMEM covers the whole K range.
+    (void)split_k;
+    (void)have_workspace;
+    if (out_tile) *out_tile = t;
+    if (out_split_k) *out_split_k = 1;
+    return kOk;
+}
+
+int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta,
+                           const float* act_scale, const void* w_scale, const void* bias, void* output, int M, int K,
+                           int N_out, float* splitk_workspace, int split_k, forge_stream_t stream, int tile) {
+    (void)splitk_workspace;
+    (void)split_k;
+    int bt = g_force_sparse_bt;
+    if (bt == 0 && tile >= 0 && tile < FORGE_SPARSE_NUM_TILES) bt = tile_to_bt(tile);
+    return sparse_gemm_dequant(W_comp, x_int8, w_meta, act_scale, H(w_scale), H(bias), H(output), M, K, N_out,
+                               S(stream), bt);
+}
+
+int forge_sparse_int8_linear_fused(int M, int K, int N_out) {
+    (void)M;
+    (void)K;
+    (void)N_out;
+    return 0;
+}
+
+int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t* w_meta, const void* w_scale,
+                             const void* bias, void* output, int M, int K, int N_out, int8_t* scratch_x_int8,
+                             float* scratch_x_scale, float* splitk_workspace, int split_k, forge_stream_t stream,
+                             int path) {
+    (void)path;
+    if (M <= 0 || K <= 0 || N_out <= 0) return kOk;
+    if (scratch_x_int8 == nullptr || scratch_x_scale == nullptr) return kBadPointer;
+    const int r = quantize_activation(H(x), scratch_x_int8, scratch_x_scale, M, K, S(stream));
+    if (r != kOk) return r;
+    return forge_sparse_int8_gemm(W_comp, scratch_x_int8, w_meta, scratch_x_scale, w_scale, bias, output, M, K, N_out,
+                                  splitk_workspace, split_k, stream, FORGE_SPARSE_TILE_AUTO);
+}
+
+int forge_splitk_reduce(const float* workspace, const void* bias, void* output, int M, int N_out,
+                        forge_stream_t stream) {
+    if (M <= 0 || N_out <= 0) return kOk;
+    if (workspace == nullptr || output == nullptr) return kBadPointer;
+    const long long total = (long long)M * N_out;
+    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, S(stream)>>>(workspace, H(bias), H(output), N_out,
+                                                                               total);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta, int32_t* output,
+                               int M, int K, int N_out, forge_stream_t stream) {
+    return sparse_gemm_s32(W_comp, x_int8, w_meta, output, M, K, N_out, S(stream), g_force_sparse_bt);
+}
+
+int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
+                            forge_stream_t stream) {
+    return prune_compress_24(weight, compressed, metadata_raw, N, K, S(stream));
+}
+
+int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, forge_stream_t stream) {
+    return pack_metadata(meta_raw, meta_packed, N, K, S(stream));
+}
+
+void forge_b200_set_dense_tile(int bn) { g_force_dense_bn = bn; }
+void forge_b200_set_sparse_tile(int bt) { g_force_sparse_bt = bt; }
+
+int forge_b200_device_status(int reset) { return read_device_status(reset); }
+
+const char* forge_b200_status_string(int status) {
+    switch (status) {
+    case kOk: return "ok";
+    case kBadShape: return "bad shape";
+    case kBadPointer: return "required pointer is null";
+    case kUnsupportedArch: return "device is not sm_100";
+    case kLaunchFailed: return "kernel launch or driver call failed";
+    case kDeviceTimeout: return "a device-side wait ran out";
+    case kTooLarge: return "exceeds a fixed capacity";
+    default: return "unknown status";
+    }
+}
+
+}  // extern "C"

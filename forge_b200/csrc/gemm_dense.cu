@@ -1,0 +1,421 @@
+// Dense INT8 GEMM for sm_100a: out[m,n] = sum_k A[m,k] * B[n,k].
+//
+// Replaces forge::gemm::int8_gemm_dequant (reference src/gemm/int8_dense.cu:26-211, a wmma
+// kernel) and adds an INT32-output form the reference only has as a host test loop
+// (tests/test_int8_dense_gemm.cu:35-39).
+//
+// Design: persistent CTAs (one per SM), each walking 128 x BN output tiles.
+//   warp 0   : TMA producer. Loads 128-byte-deep K slabs of A (128 rows) and B (BN rows)
+//              into a 4-stage shared-memory ring, 128B-swizzled, K-major.
+//   warp 1   : MMA issuer. One thread issues tcgen05.mma kind::i8 (M=128, N=BN, K=32), four per
+//              stage, accumulating s32 in TMEM; tcgen05.commit releases the stage.
+//   warps 2-5: epilogue. tcgen05.ld the accumulator (lane = output row), dequantise in
+//              registers, stage 128-byte row pieces in swizzled shared memory and TMA-store.
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "gemm_dense.cuh"
+
+namespace fb200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;   // bytes of K per stage = one 128B swizzle atom = 4 UMMAs of K=32
+constexpr int UMMA_K = 32;
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kEpiBufBytes = 32 * 128;   // one epilogue staging buffer: 32 rows x 128 bytes
+
+template <int BN>
+struct DenseCfg {
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kABytes = BLOCK_M * BLOCK_K;
+    static constexpr int kBBytes = BN * BLOCK_K;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kEpiBufs = 2;
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
+    static constexpr int kScaleBytes = 2 * BN * 2 * (int)sizeof(__half);   // [2 tiles in flight][w_scale, bias][BN]
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kScaleBytes + kBarBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory limit");
+    static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns: power of two <= 512");
+};
+
+struct TileCoord {
+    int m_blk, n_blk;
+};
+
+// Grouped raster: tiles are visited in bands of 16 row-blocks, column-block major inside a
+// band, so the tiles running concurrently share A and B slabs in L2.
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_blocks) {
+    constexpr int kGroup = 16;
+    const int band_tiles = kGroup * n_blocks;
+    const int band = t / band_tiles;
+    const int first_m = band * kGroup;
+    const int rows = min(kGroup, m_blocks - first_m);
+    const int r = t - band * band_tiles;
+    TileCoord c;
+    c.m_blk = first_m + r % rows;
+    c.n_blk = r / rows;
+    return c;
+}
+
+// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias).
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ act_scale,
+                  const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
+                  int* __restrict__ status) {
+    using Cfg = DenseCfg<BN>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+
+    uint8_t* smem_ab = smem;
+    uint8_t* smem_epi = smem + Cfg::kStages * Cfg::kStageBytes;
+    __half* smem_scale = reinterpret_cast<__half*>(smem_epi + Cfg::kEpiBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + Cfg::kEpiBytes + Cfg::kScaleBytes);
+    uint64_t* full_bar = bars;                         // [kStages]
+    uint64_t* empty_bar = bars + Cfg::kStages;         // [kStages]
+    uint64_t* tmem_full = bars + 2 * Cfg::kStages;     // [2]
+    uint64_t* tmem_empty = tmem_full + 2;              // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp_id = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled layouts need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicExch(status, 100);
+        return;
+    }
+
+    const int m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
+    const int n_blocks = (N + BN - 1) / BN;
+    const int num_tiles = m_blocks * n_blocks;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], kEpiWarps);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp_id == 0 && lane == 0) {
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_c);
+    }
+    if (warp_id == 1) {
+        tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp_id == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+                        atomicExch(status, 101);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem_ab + stage * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, tc.m_blk * BLOCK_M);
+                    tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * BN);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp_id == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(BLOCK_M, BN, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local++) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag)) {
+                    atomicExch(status, 102);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        atomicExch(status, 103);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_ab + stage * Cfg::kStageBytes);
+                    const uint64_t desc_a = make_desc_sw128(sa);
+                    const uint64_t desc_b = make_desc_sw128(sa + Cfg::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                        // advancing the start address by 32 bytes (>>4 = 2) steps one UMMA_K inside the atom
+                        umma_i8(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[stage]);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) tc_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp_id & 3;               // TMEM lane quarter this warp may read
+        const int epi_tid = (warp_id - 2) * 32 + lane;
+        uint8_t* my_stage = smem_epi + (warp_id - 2) * Cfg::kEpiBufs * kEpiBufBytes;
+        constexpr int CH = (EPI == 0) ? 32 : 64;   // output columns per 128-byte staged row
+        const bool has_bias = (bias != nullptr);
+        int local = 0;
+        int sbuf = 0;
+        // After a failed wait this warp keeps walking its tiles without touching TMEM, so it
+        // still meets the other epilogue warps at every named barrier.
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
+            const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            const int row = tc.m_blk * BLOCK_M + q * 32 + lane;
+            const int n0 = tc.n_blk * BN;
+            __half* s_ws = smem_scale + buf * 2 * BN;
+            __half* s_bias = s_ws + BN;
+            float as = 0.f;
+            if (EPI == 1) {
+                if (ok) {
+                    for (int i = epi_tid; i < BN; i += kEpiWarps * 32) {
+                        const int n = n0 + i;
+                        s_ws[i] = (n < N) ? w_scale[n] : __float2half(0.f);
+                        s_bias[i] = (has_bias && n < N) ? bias[n] : __float2half(0.f);
+                    }
+                    as = (row < M) ? act_scale[row] : 0.f;
+                }
+                named_barrier_sync(1, kEpiWarps * 32);
+            }
+            if (ok) {
+                // warp-uniform outcome: the TMEM loads below are .sync.aligned
+                ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag));
+                if (!ok) atomicExch(status, 104);
+            }
+            if (!ok) continue;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / CH; c++) {
+                uint32_t packed[32];
+                if (EPI == 0) {
+                    tmem_ld_32x32b_x32(taddr + c * CH, packed);
+                    tmem_ld_wait();
+                } else {
+                    uint32_t va[32], vb[32];
+                    tmem_ld_32x32b_x32(taddr + c * CH, va);
+                    tmem_ld_32x32b_x32(taddr + c * CH + 32, vb);
+                    tmem_ld_wait();
+                    const __half2* ws2 = reinterpret_cast<const __half2*>(s_ws + c * CH);
+                    const __half2* bs2 = reinterpret_cast<const __half2*>(s_bias + c * CH);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 w = __half22float2(ws2[i]);
+                        const float2 b = __half22float2(bs2[i]);
+                        packed[i] = pack_half2(
+                            dequant_gemm(static_cast<int>(va[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
+                            dequant_gemm(static_cast<int>(va[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 w = __half22float2(ws2[16 + i]);
+                        const float2 b = __half22float2(bs2[16 + i]);
+                        packed[16 + i] = pack_half2(
+                            dequant_gemm(static_cast<int>(vb[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
+                            dequant_gemm(static_cast<int>(vb[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                    }
+                }
+                uint8_t* stg = my_stage + sbuf * kEpiBufBytes;
+                // the TMA store that last read this buffer must be done with it
+                if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int chunk = j ^ (lane & 7);   // 128B swizzle: 16-byte chunk index XOR row%8
+                    *reinterpret_cast<uint4*>(stg + lane * 128 + chunk * 16) =
+                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tm_c, stg, n0 + c * CH, tc.m_blk * BLOCK_M + q * 32);
+                    tma_store_commit();
+                }
+                sbuf = (sbuf + 1) % Cfg::kEpiBufs;
+            }
+            // accumulator fully read: hand the TMEM buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        // give loads still in flight time to land before the CTA's shared memory is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp_id == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Plain-CUDA kernel for shapes the TMA path cannot describe (K or N not a multiple of the
+// 16-byte TMA stride granule, misaligned base pointers). One thread per output element.
+template <int EPI>
+__global__ void dense_gemm_ragged_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                                         const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
+                                         const __half* __restrict__ bias, void* __restrict__ out, int M, int N,
+                                         int K) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)M * N) return;
+    const int m = (int)(idx / N), n = (int)(idx % N);
+    const int8_t* a = A + (size_t)m * K;
+    const int8_t* b = B + (size_t)n * K;
+    int acc = 0;
+    for (int k = 0; k < K; k++) acc += (int)a[k] * (int)b[k];
+    if (EPI == 0) {
+        reinterpret_cast<int32_t*>(out)[idx] = acc;
+    } else {
+        const float s = mul_ftz(act_scale[m], __half2float(w_scale[n]));
+        const float o = dequant_gemm(acc, s, bias ? __half2float(bias[n]) : 0.f, bias != nullptr);
+        reinterpret_cast<__half*>(out)[idx] = __float2half_rn(o);
+    }
+}
+
+template <int BN, int EPI>
+int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale, const __half* bias,
+                 void* out, int M, int K, int N, cudaStream_t stream) {
+    using Cfg = DenseCfg<BN>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = dense_gemm_kernel<BN, EPI>;
+    if (!attr_set[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+            return kLaunchFailed;
+        attr_set[dev & 63] = true;
+    }
+    CUtensorMap tm_a, tm_b, tm_c;
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {BLOCK_K, BLOCK_M};
+        if (!make_tmap(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {BLOCK_K, BN};
+        if (!make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t esz = (EPI == 0) ? 4 : 2;
+        const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)N * esz};
+        const uint32_t box[2] = {(uint32_t)(128 / esz), 32};
+        const CUtensorMapDataType dt = (EPI == 0) ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if (!make_tmap(&tm_c, dt, 2, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return kLaunchFailed;
+    }
+    int* status = status_word();
+    if (status == nullptr) return kLaunchFailed;
+    const int m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
+    const int n_blocks = (N + BN - 1) / BN;
+    const long long tiles = (long long)m_blocks * n_blocks;
+    const int grid = (int)std::min<long long>(tiles, sm_count());
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, tm_c, act_scale, w_scale, bias, M, N, K, status);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+template <int EPI>
+int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
+                   const __half* bias, void* out, int M, int K, int N, cudaStream_t stream, int force_bn) {
+    if (M <= 0 || K <= 0 || N <= 0) return kOk;   // reference: silent no-op (int8_dense.cu:195)
+    if (A == nullptr || B == nullptr || out == nullptr) return kBadPointer;
+    if (EPI == 1 && (act_scale == nullptr || w_scale == nullptr)) return kBadPointer;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    const int out_esz = (EPI == 0) ? 4 : 2;
+    const bool tma_ok = (K % 16 == 0) && ((long long)N * out_esz % 16 == 0) && aligned16(A) && aligned16(B) &&
+                        aligned16(out);
+    if (!tma_ok) {
+        const long long total = (long long)M * N;
+        const int block = 256;
+        const long long grid = (total + block - 1) / block;
+        dense_gemm_ragged_kernel<EPI><<<(unsigned)grid, block, 0, stream>>>(A, B, act_scale, w_scale, bias, out, M,
+                                                                           N, K);
+        return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+    // Tile width: the widest tile that still gives every SM work.
+    int bn = force_bn;
+    if (bn != 64 && bn != 128 && bn != 256) {
+        const long long m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
+        const int sms = sm_count();
+        if (m_blocks * ((N + 255) / 256) >= sms) bn = 256;
+        else if (m_blocks * ((N + 127) / 128) >= sms) bn = 128;
+        else bn = 64;
+    }
+    switch (bn) {
+    case 256: return launch_dense<256, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    case 128: return launch_dense<128, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    default:  return launch_dense<64, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    }
+}
+
+}  // namespace
+
+int dense_gemm_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K, int N, cudaStream_t stream,
+                   int force_bn) {
+    return dense_dispatch<0>(A, B, nullptr, nullptr, nullptr, out, M, K, N, stream, force_bn);
+}
+
+int dense_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
+                       const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream, int force_bn) {
+    return dense_dispatch<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream, force_bn);
+}
+
+}  // namespace fb200

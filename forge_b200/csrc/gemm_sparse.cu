@@ -1,0 +1,439 @@
+// 2:4 structured-sparse INT8 GEMM for sm_100a:
+//   out[m, n] = sum_k W24[n, k] * x[m, k]      (W24 = the 2:4-pruned weight)
+// from the compressed weight W_comp (N_out, K/2), the packed metadata w_meta (N_out, K/32)
+// and int8 activations x (M, K).
+//
+// Replaces forge::gemm::sparse_int8_gemm (reference src/gemm/int8_sparse.cu:139-720, 960-1003,
+// a warp-synchronous mma.sp kernel) and adds an INT32-output form.
+//
+// Design: persistent CTAs walking tiles of 128 weight rows x BT tokens. The sparse operand
+// must be the A operand of tcgen05.mma.sp, so weight rows sit on the TMEM lanes and the
+// accumulator is the transpose of the output tile.
+//   warp 0   : TMA producer. Per 256-deep K slab: compressed weights (128 rows x 128 bytes,
+//              128B swizzle), activations (two 128-byte-wide swizzled atoms of BT rows) and the
+//              metadata slab (128 rows x 32 bytes, fetched as two 16-byte columns so that it
+//              lands as unswizzled 8-row x 16-byte core matrices).
+//   warp 1   : MMA issuer. tcgen05.cp moves the metadata into TMEM - the public w_meta layout
+//              (row-major uint32, nibble g at bits [4g,4g+4)) is already what the tensor core
+//              expects per lane: 2 columns per 64-deep step - then four
+//              tcgen05.mma.sp kind::i8 (M=128, N=BT, K=64) per slab.
+//   warps 2-5: epilogue. tcgen05.ld (lane = weight row, registers = tokens), dequantise,
+//              transpose through shared memory ([token][weight row]) and TMA-store.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "gemm_dense.cuh"
+#include "gemm_sparse.cuh"
+
+namespace fb200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BW = 128;          // weight rows per tile (UMMA M)
+constexpr int SLAB_K = 256;      // logical K per pipeline stage
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kMetaBytes = BW * 32;        // 128 rows x 32 bytes per slab
+constexpr int kStageOutBytes = 16 * 1024;  // epilogue staging, used as two 8 KB halves
+
+template <int BT>
+struct SparseCfg {
+    static constexpr int kABytes = BW * 128;
+    static constexpr int kBAtomBytes = BT * 128;
+    static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
+    static constexpr int kAccBufs = (2 * BT + 32 <= 512) ? 2 : 1;
+    static constexpr int kScaleBytes = 2 * BT * (int)sizeof(float);
+    static constexpr int kBarBytes = 256;
+    static constexpr int kFixed = kStageOutBytes + kScaleBytes + kBarBytes;
+    static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesMax > 8 ? 8 : kStagesMax;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
+    static constexpr int kMetaCols = 8 * kStages;             // 8 TMEM columns of metadata per stage
+    static constexpr int kAccCols = kAccBufs * BT;
+    static constexpr int kTmemNeed = kAccCols + kMetaCols;
+    static constexpr int kTmemCols = kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128 : kTmemNeed <= 256 ? 256 : 512;
+    static_assert(kStages >= 2, "pipeline needs at least two stages");
+    static_assert(kTmemNeed <= 512, "TMEM capacity");
+    static_assert(kStageBytes % 1024 == 0, "stage buffers must keep 1024-byte alignment");
+};
+
+struct TileCoord {
+    int w_blk, t_blk;
+};
+
+// Bands of 8 weight-row blocks, token-block major inside a band: concurrently running tiles
+// share weight slabs and activation slabs in L2.
+__device__ __forceinline__ TileCoord tile_coord(int t, int w_blocks, int t_blocks) {
+    constexpr int kGroup = 8;
+    const int band_tiles = kGroup * t_blocks;
+    const int band = t / band_tiles;
+    const int first_w = band * kGroup;
+    const int rows = min(kGroup, w_blocks - first_w);
+    const int r = t - band * band_tiles;
+    TileCoord c;
+    c.w_blk = first_w + r % rows;
+    c.t_blk = r / rows;
+    return c;
+}
+
+// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias).
+template <int BT, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_out,
+                   const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
+                   const __half* __restrict__ bias, int M, int N_out, int K, int* __restrict__ status) {
+    using Cfg = SparseCfg<BT>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+
+    uint8_t* smem_stage = smem;
+    uint8_t* smem_out = smem + Cfg::kStages * Cfg::kStageBytes;
+    float* smem_as = reinterpret_cast<float*>(smem_out + kStageOutBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_out + kStageOutBytes + Cfg::kScaleBytes);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + Cfg::kStages;
+    uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp_id = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(status, 200);
+        return;
+    }
+
+    const int w_blocks = (N_out + BW - 1) / BW;
+    const int t_blocks = (M + BT - 1) / BT;
+    const int num_tiles = w_blocks * t_blocks;
+    const int num_kb = (K + SLAB_K - 1) / SLAB_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp_id == 0 && lane == 0) {
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_x);
+        prefetch_tensormap(&tm_meta);
+        prefetch_tensormap(&tm_out);
+    }
+    if (warp_id == 1) {
+        tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
+
+    if (warp_id == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+                        atomicExch(status, 201);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
+                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), tc.w_blk * BW);
+                    tma_load_2d(sb, &tm_x, &full_bar[stage], kb * SLAB_K, tc.t_blk * BT);
+                    tma_load_2d(sb + Cfg::kBAtomBytes, &tm_x, &full_bar[stage], kb * SLAB_K + 128, tc.t_blk * BT);
+                    tma_load_3d(sm, &tm_meta, &full_bar[stage], 0, tc.w_blk * BW, kb * 2);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp_id == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(BW, BT, true);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local++) {
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag)) {
+                    atomicExch(status, 202);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * BT;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        atomicExch(status, 203);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_stage + stage * Cfg::kStageBytes);
+                    const uint32_t sb = sa + Cfg::kABytes;
+                    const uint32_t sm = sb + 2 * Cfg::kBAtomBytes;
+                    const uint32_t te = tmem_meta + 8 * stage;
+                    // metadata: two 16-byte columns of 128 rows -> 2 x 4 TMEM columns
+                    tmem_cp_128x128b(te, make_desc_noswizzle(sm, 2048, 128));
+                    tmem_cp_128x128b(te + 4, make_desc_noswizzle(sm + 2048, 2048, 128));
+                    const uint64_t desc_a = make_desc_sw128(sa);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // step j: 32 compressed bytes of A, 64 bytes of B (atom j/2, half j%2), 2 metadata columns
+                        const uint64_t desc_b = make_desc_sw128(sb + (j >> 1) * Cfg::kBAtomBytes) + 4 * (j & 1);
+                        umma_i8_sp(tmem_acc, desc_a + 2 * j, desc_b, te + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[stage]);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) tc_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp_id & 3;
+        const int epi_tid = (warp_id - 2) * 32 + lane;
+        constexpr int TOK = (EPI == 0) ? 16 : 32;              // tokens per staged chunk (8 KB)
+        constexpr int ROW_BYTES = BW * ((EPI == 0) ? 4 : 2);   // one token's 128 outputs
+        const bool has_bias = (bias != nullptr);
+        int local = 0;
+        int half = 0;
+        bool ok = true;   // after a failed wait: keep meeting the named barriers, touch nothing
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
+            const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
+            const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+            const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+            const int n = tc.w_blk * BW + q * 32 + lane;   // this thread's weight row = output column
+            const int m0 = tc.t_blk * BT;
+            float* s_as = smem_as + (local & 1) * BT;
+            float ws = 0.f, bs = 0.f;
+            if (EPI == 1) {
+                if (ok) {
+                    for (int i = epi_tid; i < BT; i += kEpiThreads) s_as[i] = (m0 + i < M) ? act_scale[m0 + i] : 0.f;
+                    if (n < N_out) {
+                        ws = __half2float(w_scale[n]);
+                        if (has_bias) bs = __half2float(bias[n]);
+                    }
+                }
+                named_barrier_sync(1, kEpiThreads);
+            }
+            if (ok) {
+                // warp-uniform outcome: the TMEM loads below are .sync.aligned
+                ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag));
+                if (!ok) atomicExch(status, 204);
+            }
+            if (ok) tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+            for (int c = 0; c < BT / 32; c++) {
+                uint32_t v[32];
+                if (ok) {
+                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int h = 0; h < 32 / TOK; h++) {
+                    uint8_t* stg = smem_out + half * (kStageOutBytes / 2);
+                    // the TMA store that last read this half must be done with it
+                    if (epi_tid == 0) tma_store_wait_read<1>();
+                    named_barrier_sync(2, kEpiThreads);
+                    if (ok) {
+#pragma unroll
+                        for (int j = 0; j < TOK; j++) {
+                            const int tok = c * 32 + h * TOK + j;
+                            const int acc = static_cast<int>(v[h * TOK + j]);
+                            if (EPI == 0) {
+                                *reinterpret_cast<int32_t*>(stg + j * ROW_BYTES + (q * 32 + lane) * 4) = acc;
+                            } else {
+                                const float o = dequant_gemm(acc, mul_ftz(s_as[tok], ws), bs, has_bias);
+                                *reinterpret_cast<__half*>(stg + j * ROW_BYTES + (q * 32 + lane) * 2) =
+                                    __float2half_rn(o);
+                            }
+                        }
+                        fence_proxy_async_smem();
+                    }
+                    named_barrier_sync(3, kEpiThreads);
+                    if (ok && epi_tid == 0) {
+                        tma_store_2d(&tm_out, stg, tc.w_blk * BW, m0 + c * 32 + h * TOK);
+                        tma_store_commit();
+                    }
+                    half ^= 1;
+                }
+            }
+            if (ok) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            }
+        }
+        if (epi_tid == 0) tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp_id == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Plain-CUDA kernel for shapes the TMA path cannot describe (K % 128 != 0, misaligned
+// pointers or row pitches). One thread per output element, decoding the nibbles directly.
+template <int EPI>
+__global__ void sparse_gemm_ragged_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restrict__ x,
+                                          const uint32_t* __restrict__ w_meta, const float* __restrict__ act_scale,
+                                          const __half* __restrict__ w_scale, const __half* __restrict__ bias,
+                                          void* __restrict__ out, int M, int K, int N_out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)M * N_out) return;
+    const int m = (int)(idx / N_out), n = (int)(idx % N_out);
+    const int8_t* wc = W_comp + (size_t)n * (K / 2);
+    const uint32_t* me = w_meta + (size_t)n * (K / 32);
+    const int8_t* xr = x + (size_t)m * K;
+    int acc = 0;
+    for (int g = 0; g < K / 4; g++) {
+        const uint32_t nib = (me[g >> 3] >> (4 * (g & 7))) & 0xF;
+        acc += (int)wc[2 * g] * (int)xr[4 * g + (nib & 3)] + (int)wc[2 * g + 1] * (int)xr[4 * g + (nib >> 2)];
+    }
+    if (EPI == 0) {
+        reinterpret_cast<int32_t*>(out)[idx] = acc;
+    } else {
+        const float s = mul_ftz(act_scale[m], __half2float(w_scale[n]));
+        const float o = dequant_gemm(acc, s, bias ? __half2float(bias[n]) : 0.f, bias != nullptr);
+        reinterpret_cast<__half*>(out)[idx] = __float2half_rn(o);
+    }
+}
+
+template <int BT, int EPI>
+int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                  const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
+                  cudaStream_t stream) {
+    using Cfg = SparseCfg<BT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = sparse_gemm_kernel<BT, EPI>;
+    if (!attr_set[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+            return kLaunchFailed;
+        attr_set[dev & 63] = true;
+    }
+    CUtensorMap tm_w, tm_x, tm_meta, tm_out;
+    {
+        const uint64_t dims[2] = {(uint64_t)K / 2, (uint64_t)N_out};
+        const uint64_t str[1] = {(uint64_t)K / 2};
+        const uint32_t box[2] = {128, BW};
+        if (!make_tmap(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W_comp, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {128, BT};
+        if (!make_tmap(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        // (4 words, N_out rows, K/128 column groups): one box = 2 column groups of 128 rows x 16 bytes
+        const uint64_t dims[3] = {4, (uint64_t)N_out, (uint64_t)K / 128};
+        const uint64_t str[2] = {(uint64_t)K / 8, 16};
+        const uint32_t box[3] = {4, BW, 2};
+        if (!make_tmap(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w_meta, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t esz = (EPI == 0) ? 4 : 2;
+        const uint64_t dims[2] = {(uint64_t)N_out, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)N_out * esz};
+        const uint32_t box[2] = {BW, (uint32_t)((EPI == 0) ? 16 : 32)};
+        const CUtensorMapDataType dt = (EPI == 0) ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if (!make_tmap(&tm_out, dt, 2, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kLaunchFailed;
+    }
+    int* status = status_word();
+    if (status == nullptr) return kLaunchFailed;
+    const long long tiles = (long long)((N_out + BW - 1) / BW) * ((M + BT - 1) / BT);
+    const int grid = (int)std::min<long long>(tiles, sm_count());
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_out, act_scale, w_scale, bias, M,
+                                                      N_out, K, status);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+template <int EPI>
+int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                    const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
+                    cudaStream_t stream, int force_bt) {
+    if (M <= 0 || K <= 0 || N_out <= 0) return kOk;   // reference: silent no-op (int8_sparse.cu:976)
+    if (W_comp == nullptr || x == nullptr || w_meta == nullptr || out == nullptr) return kBadPointer;
+    if (EPI == 1 && (act_scale == nullptr || w_scale == nullptr)) return kBadPointer;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    const int out_esz = (EPI == 0) ? 4 : 2;
+    const bool tma_ok = (K % 128 == 0) && ((long long)N_out * out_esz % 16 == 0) && aligned16(W_comp) &&
+                        aligned16(x) && aligned16(w_meta) && aligned16(out);
+    if (!tma_ok) {
+        const long long total = (long long)M * N_out;
+        sparse_gemm_ragged_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+            W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
+        return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+    int bt = force_bt;
+    if (bt != 32 && bt != 64 && bt != 128) {
+        const long long w_blocks = (N_out + BW - 1) / BW;
+        const int sms = sm_count();
+        if (M > 64 && w_blocks * ((M + 127) / 128) >= sms) bt = 128;
+        else if (M > 32) bt = (M > 64 && w_blocks * ((M + 63) / 64) < sms) ? 64 : (M > 64 ? 128 : 64);
+        else bt = 32;
+    }
+    switch (bt) {
+    case 128: return launch_sparse<128, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    case 64:  return launch_sparse<64, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    default:  return launch_sparse<32, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    }
+}
+
+}  // namespace
+
+int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,
+                    int N_out, cudaStream_t stream, int force_bt) {
+    return sparse_dispatch<0>(W_comp, x, w_meta, nullptr, nullptr, nullptr, out, M, K, N_out, stream, force_bt);
+}
+
+int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                        const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
+                        cudaStream_t stream, int force_bt) {
+    return sparse_dispatch<1>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream, force_bt);
+}
+
+}  // namespace fb200

@@ -1,0 +1,19 @@
+// Internal declarations of the 2:4-sparse INT8 GEMM launchers (gemm_sparse.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace fb200 {
+
+// out (M,N_out) s32 = x (M,K) s8 x W24 (N_out,K)^T, W24 given as W_comp (N_out,K/2) + w_meta (N_out,K/32).
+// force_bt: 32/64/128 pins the token-tile width, anything else selects it automatically.
+int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,
+                    int N_out, cudaStream_t stream, int force_bt);
+
+// out (M,N_out) fp16 = fp16((act_scale[m] * w_scale[n]) * acc + bias[n]).
+int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                        const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
+                        cudaStream_t stream, int force_bt);
+
+}  // namespace fb200

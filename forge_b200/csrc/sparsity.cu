@@ -1,0 +1,180 @@
+// 2:4 magnitude prune + compress, and metadata packing, for sm_100a.
+//
+// Replaces forge::sparsity::prune_compress_24 (reference src/sparsity/prune_compress.cu:9-85)
+// and forge::sparsity::pack_metadata (reference src/sparsity/pack_metadata.cu:8-44). Outputs are
+// byte-identical to the reference: per group of 4 along K the two smallest magnitudes are
+// dropped (scan order and strict '<' comparisons as in prune_compress.cu:39-50), the two kept
+// values are stored in ascending position order, and the group's nibble is idx0 | idx1 << 2;
+// pack_metadata puts nibble g of each run of 8 at bits [4g, 4g+4) of one uint32.
+//
+// Both are HBM-bound streaming kernels; the launchers use 16-byte accesses (8 groups, or 16
+// nibbles, per thread) whenever the shape and pointers allow it.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace fb200 {
+
+// Decides one group of four signed bytes packed in `w` (byte i = position i).
+// Returns the nibble; `kept` receives the two surviving bytes (low byte = lower position).
+__device__ __forceinline__ uint32_t prune_group(uint32_t w, uint32_t& kept) {
+    int a[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) a[i] = abs((int)(int8_t)((w >> (8 * i)) & 0xFF));
+    int min1 = 0, min2 = 1;
+    if (a[0] > a[1]) {
+        min1 = 1;
+        min2 = 0;
+    }
+#pragma unroll
+    for (int i = 2; i < 4; i++) {
+        const int a1 = (min1 == 0) ? a[0] : (min1 == 1) ? a[1] : (min1 == 2) ? a[2] : a[3];
+        const int a2 = (min2 == 0) ? a[0] : (min2 == 1) ? a[1] : (min2 == 2) ? a[2] : a[3];
+        if (a[i] < a1) {
+            min2 = min1;
+            min1 = i;
+        } else if (a[i] < a2) {
+            min2 = i;
+        }
+    }
+    const uint32_t drop = (1u << min1) | (1u << min2);
+    const uint32_t keep = ~drop & 0xFu;            // exactly two bits set
+    const int k0 = __ffs(keep) - 1;                // lower kept position
+    const int k1 = 31 - __clz(keep);               // higher kept position
+    kept = ((w >> (8 * k0)) & 0xFF) | (((w >> (8 * k1)) & 0xFF) << 8);
+    return (uint32_t)(k0 | (k1 << 2));
+}
+
+}  // namespace fb200
+
+// Public kernel declarations of the reference headers (include/forge/sparsity/prune_compress.cuh:16-21,
+// include/forge/sparsity/pack_metadata.cuh:15-19): one thread per group / per output word.
+namespace forge { namespace sparsity {
+
+__global__ void prune_compress_kernel(const int8_t* __restrict__ weight, int8_t* __restrict__ compressed,
+                                      uint8_t* __restrict__ metadata_raw, int N, int K) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int groups_per_row = K / 4;
+    const long long total = (long long)N * groups_per_row;
+    if (idx >= total) return;
+    const long long row = idx / groups_per_row;
+    const int group = (int)(idx - row * groups_per_row);
+    const int8_t* p = weight + row * K + group * 4;
+    const uint32_t w = (uint32_t)(uint8_t)p[0] | ((uint32_t)(uint8_t)p[1] << 8) | ((uint32_t)(uint8_t)p[2] << 16) |
+                       ((uint32_t)(uint8_t)p[3] << 24);
+    uint32_t kept;
+    const uint32_t nib = fb200::prune_group(w, kept);
+    int8_t* c = compressed + row * (K / 2) + group * 2;
+    c[0] = (int8_t)(kept & 0xFF);
+    c[1] = (int8_t)(kept >> 8);
+    metadata_raw[idx] = (uint8_t)nib;
+}
+
+__global__ void pack_metadata_kernel(const uint8_t* __restrict__ meta_raw, uint32_t* __restrict__ meta_packed, int N,
+                                     int K) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int groups_per_row = K / 4;
+    const int chunks_per_row = K / 32;
+    const long long total = (long long)N * chunks_per_row;
+    if (idx >= total) return;
+    const long long row = idx / chunks_per_row;
+    const int chunk = (int)(idx - row * chunks_per_row);
+    const uint8_t* p = meta_raw + row * groups_per_row + chunk * 8;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int g = 0; g < 8; g++) packed |= ((uint32_t)(p[g] & 0xF)) << (g * 4);
+    meta_packed[idx] = packed;
+}
+
+}}  // namespace forge::sparsity
+
+namespace fb200 {
+
+namespace {
+
+// 32 weight bytes (8 groups) per thread -> 16 compressed bytes + 8 nibble bytes.
+// Valid when K % 4 == 0 (groups tile the flat array) and N*K % 32 == 0.
+__global__ void __launch_bounds__(256)
+prune_compress_vec_kernel(const uint4* __restrict__ weight, uint4* __restrict__ compressed,
+                          uint2* __restrict__ metadata_raw, long long nthreads) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= nthreads) return;
+    const uint4 w0 = __ldcs(weight + 2 * id), w1 = __ldcs(weight + 2 * id + 1);
+    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    uint32_t comp[4] = {0u, 0u, 0u, 0u};
+    uint32_t meta[2] = {0u, 0u};
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+        uint32_t kept;
+        const uint32_t nib = prune_group(w[g], kept);
+        comp[g >> 1] |= kept << (16 * (g & 1));
+        meta[g >> 2] |= nib << (8 * (g & 3));
+    }
+    compressed[id] = make_uint4(comp[0], comp[1], comp[2], comp[3]);
+    metadata_raw[id] = make_uint2(meta[0], meta[1]);
+}
+
+// 16 nibble bytes per thread -> two packed words. Valid when K % 32 == 0 and N*K/4 % 16 == 0.
+__global__ void __launch_bounds__(256)
+pack_metadata_vec_kernel(const uint4* __restrict__ meta_raw, uint2* __restrict__ meta_packed, long long nthreads) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= nthreads) return;
+    const uint4 r = __ldcs(meta_raw + id);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    uint32_t out[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint32_t p = 0;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint32_t x = w[2 * h + j] & 0x0F0F0F0Fu;   // four nibbles, one per byte
+            const uint32_t four = (x & 0xF) | ((x >> 4) & 0xF0) | ((x >> 8) & 0xF00) | ((x >> 12) & 0xF000);
+            p |= four << (16 * j);
+        }
+        out[h] = p;
+    }
+    meta_packed[id] = make_uint2(out[0], out[1]);
+}
+
+}  // namespace
+
+int prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
+                      cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return kOk;   // reference: silent no-op (prune_compress.cu:79)
+    if (weight == nullptr || compressed == nullptr || metadata_raw == nullptr) return kBadPointer;
+    const long long bytes = (long long)N * K;
+    const bool vec_ok = (K % 4 == 0) && (bytes % 32 == 0) && aligned16(weight) && aligned16(compressed) &&
+                        (reinterpret_cast<uintptr_t>(metadata_raw) % 8 == 0);
+    if (vec_ok) {
+        const long long n = bytes / 32;
+        prune_compress_vec_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint4*>(weight), reinterpret_cast<uint4*>(compressed),
+            reinterpret_cast<uint2*>(metadata_raw), n);
+    } else {
+        const long long groups = (long long)N * (K / 4);
+        if (groups == 0) return kOk;
+        forge::sparsity::prune_compress_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(
+            weight, compressed, metadata_raw, N, K);
+    }
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+int pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return kOk;   // reference: silent no-op (pack_metadata.cu:38)
+    if (meta_raw == nullptr || meta_packed == nullptr) return kBadPointer;
+    const long long nibbles = (long long)N * (K / 4);
+    const bool vec_ok = (K % 32 == 0) && (nibbles % 16 == 0) && aligned16(meta_raw) &&
+                        (reinterpret_cast<uintptr_t>(meta_packed) % 8 == 0);
+    if (vec_ok) {
+        const long long n = nibbles / 16;
+        pack_metadata_vec_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint4*>(meta_raw), reinterpret_cast<uint2*>(meta_packed), n);
+    } else {
+        const long long words = (long long)N * (K / 32);
+        if (words == 0) return kOk;
+        forge::sparsity::pack_metadata_kernel<<<(unsigned)((words + 255) / 256), 256, 0, stream>>>(meta_raw,
+                                                                                                  meta_packed, N, K);
+    }
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+}  // namespace fb200

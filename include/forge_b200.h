@@ -1,0 +1,162 @@
+/* forge_b200 - C ABI of the B200 (sm_100a) implementation of Forge's quantized-inference path.
+ *
+ * Every entry point takes plain device pointers, int shapes and a CUDA stream, enqueues its
+ * work on that stream and returns without synchronising. Buffers are caller-owned; nothing
+ * is allocated. Return value: 0 on success, otherwise a FORGE_B200_* status code. Sizes
+ * <= 0 are a silent no-op that returns 0, as in the reference launchers.
+ *
+ * FP16 buffers are passed as `const void*` / `void*` (IEEE binary16, the layout of CUDA's
+ * __half) so that this header stays plain C. `forge_stream_t` is a cudaStream_t.
+ *
+ * Each declaration names the reference interface it stands in for (path:line inside the
+ * Forge source tree).
+ */
+#ifndef FORGE_B200_H
+#define FORGE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* forge_stream_t;
+
+enum {
+    FORGE_B200_OK = 0,
+    FORGE_B200_BAD_SHAPE = 1,
+    FORGE_B200_BAD_POINTER = 2,
+    FORGE_B200_UNSUPPORTED_ARCH = 3, /* the current device is not compute capability 10.x */
+    FORGE_B200_LAUNCH_FAILED = 4,
+    FORGE_B200_DEVICE_TIMEOUT = 5,   /* a bounded device-side wait ran out */
+    FORGE_B200_TOO_LARGE = 6
+};
+
+/* ---------------------------------------------------------------- forge::quant */
+
+/* forge::quant::fused_quantize_activation - include/forge/quant/quantize.cuh:23-29,
+ * src/quant/quantize.cu:162-191. input (M,K) fp16 -> output (M,K) int8 + scales (M) fp32. */
+int forge_fused_quantize_activation(const void* input, int8_t* output, float* scales, int M, int K,
+                                    forge_stream_t stream);
+
+/* forge::quant::fused_dequantize_bias - include/forge/quant/dequantize.cuh:22-30,
+ * src/quant/dequantize.cu:30-45. input (M,N) int32, act_scale (M) fp32, w_scale/bias (N) fp16
+ * (bias may be NULL) -> output (M,N) fp16. */
+int forge_fused_dequantize_bias(const int32_t* input, const float* act_scale, const void* w_scale, const void* bias,
+                                void* output, int M, int N, forge_stream_t stream);
+
+/* ---------------------------------------------------------------- forge::gemm, dense */
+
+/* forge::gemm::int8_gemm_dequant - include/forge/gemm/int8_dense.cuh:24-34,
+ * src/gemm/int8_dense.cu:183-211. A (M,K) int8, B (N,K) int8 -> output (M,N) fp16 =
+ * fp16((act_scale[m]*w_scale[n]) * sum_k A[m,k]B[n,k] + bias[n]). */
+int forge_int8_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
+                            const void* bias, void* output, int M, int K, int N, forge_stream_t stream);
+
+/* forge::gemm::int8_gemm - include/forge/gemm/int8_gemm.cuh:25-35, src/gemm/int8_gemm.cu:27-46
+ * (the reference dispatches on compute capability; here there is one backend). */
+int forge_int8_gemm(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale, const void* bias,
+                    void* output, int M, int K, int N, forge_stream_t stream);
+
+/* forge::gemm::int8_dp4a_gemm_dequant - include/forge/gemm/int8_dp4a.cuh:25-35. Kept so callers
+ * link; runs the same tensor-core kernel as forge_int8_gemm_dequant. */
+int forge_int8_dp4a_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
+                                 const void* bias, void* output, int M, int K, int N, forge_stream_t stream);
+
+/* forge::gemm::int8_linear - include/forge/gemm/int8_dense.cuh:37-48, src/gemm/int8_dense.cu:213-232.
+ * x (M,K) fp16 -> quantize into scratch_a_int8 (M,K) / scratch_a_scale (M) -> GEMM + dequant. */
+int forge_int8_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
+                      int M, int K, int N, int8_t* scratch_a_int8, float* scratch_a_scale, forge_stream_t stream);
+
+/* forge::gemm::int8_dp4a_linear - include/forge/gemm/int8_dp4a.cuh:38-50. Same as forge_int8_linear. */
+int forge_int8_dp4a_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
+                           int M, int K, int N, int8_t* scratch_a_int8, float* scratch_a_scale,
+                           forge_stream_t stream);
+
+/* forge::gemm::get_compute_capability / has_wmma_int8 - include/forge/gemm/int8_gemm.cuh:18-21.
+ * Unlike the reference (one cached value for all devices) the answer is per device. */
+int forge_get_compute_capability(int device);
+int forge_has_wmma_int8(int device);
+
+/* Additive: raw INT32 GEMM output (M,N). The reference computes this only in its host test
+ * loop, tests/test_int8_dense_gemm.cu:35-39. */
+int forge_int8_gemm_s32(const int8_t* A, const int8_t* B, int32_t* output, int M, int K, int N,
+                        forge_stream_t stream);
+
+/* ---------------------------------------------------------------- forge::gemm, 2:4 sparse */
+
+/* Tile / path ids of include/forge/gemm/int8_sparse.cuh:26-31,74-76. */
+enum {
+    FORGE_SPARSE_TILE_AUTO = -1,
+    FORGE_SPARSE_TILE_256x128 = 0,
+    FORGE_SPARSE_TILE_128x128 = 1,
+    FORGE_SPARSE_TILE_128x64 = 2,
+    FORGE_SPARSE_NUM_TILES = 3,
+    FORGE_SPARSE_LINEAR_AUTO = -1,
+    FORGE_SPARSE_LINEAR_TWO_PASS = 0,
+    FORGE_SPARSE_LINEAR_FUSED = 1
+};
+
+/* forge::gemm::sparse_int8_gemm_plan - include/forge/gemm/int8_sparse.cuh:33-50,
+ * src/gemm/int8_sparse.cu:875-920. Writes the (tile, split_k) forge_sparse_int8_gemm will run. */
+int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_workspace, int tile, int* out_tile,
+                                int* out_split_k);
+
+/* forge::gemm::sparse_int8_gemm - include/forge/gemm/int8_sparse.cuh:57-71,
+ * src/gemm/int8_sparse.cu:960-1003. W_comp (N_out,K/2) int8, x_int8 (M,K) int8,
+ * w_meta (N_out,K/32) uint32 -> output (M,N_out) fp16. splitk_workspace: optional (M,N_out)
+ * 4-byte-element buffer, overwritten by the call. */
+int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta,
+                           const float* act_scale, const void* w_scale, const void* bias, void* output, int M, int K,
+                           int N_out, float* splitk_workspace, int split_k, forge_stream_t stream, int tile);
+
+/* forge::gemm::sparse_int8_linear_fused - include/forge/gemm/int8_sparse.cuh:78-83. 1 or 0. */
+int forge_sparse_int8_linear_fused(int M, int K, int N_out);
+
+/* forge::gemm::sparse_int8_linear - include/forge/gemm/int8_sparse.cuh:90-105,
+ * src/gemm/int8_sparse.cu:1005-1043. */
+int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t* w_meta, const void* w_scale,
+                             const void* bias, void* output, int M, int K, int N_out, int8_t* scratch_x_int8,
+                             float* scratch_x_scale, float* splitk_workspace, int split_k, forge_stream_t stream,
+                             int path);
+
+/* forge::gemm::splitk_reduce - include/forge/gemm/int8_sparse.cuh:108-114,
+ * src/gemm/int8_sparse.cu:945-958. output = fp16(workspace + bias[n]). */
+int forge_splitk_reduce(const float* workspace, const void* bias, void* output, int M, int N_out,
+                        forge_stream_t stream);
+
+/* Additive: raw INT32 output (M,N_out) of the 2:4-sparse GEMM (the reference checks it only
+ * through an FP64 host loop, tests/test_int8_sparse_gemm.cu:69-80). */
+int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta, int32_t* output,
+                               int M, int K, int N_out, forge_stream_t stream);
+
+/* ---------------------------------------------------------------- forge::sparsity */
+
+/* forge::sparsity::prune_compress_24 - include/forge/sparsity/prune_compress.cuh:23-30,
+ * src/sparsity/prune_compress.cu:71-85. weight (N,K) int8 -> compressed (N,K/2) int8 +
+ * metadata_raw (N*K/4) one nibble per byte. */
+int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
+                            forge_stream_t stream);
+
+/* forge::sparsity::pack_metadata - include/forge/sparsity/pack_metadata.cuh:21-26,
+ * src/sparsity/pack_metadata.cu:32-44. meta_raw (N*K/4) -> meta_packed (N,K/32) uint32. */
+int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, forge_stream_t stream);
+
+/* ---------------------------------------------------------------- diagnostics (additive) */
+
+/* Tuning/testing knobs: pin the dense tile width (64/128/256) or the sparse token-tile width
+ * (32/64/128); 0 restores automatic selection. Process-wide. */
+void forge_b200_set_dense_tile(int bn);
+void forge_b200_set_sparse_tile(int bt);
+
+/* Reads (and, if reset != 0, clears) the device status word of the current device. 0 means no
+ * kernel gave up on a wait; synchronises the device. */
+int forge_b200_device_status(int reset);
+
+const char* forge_b200_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FORGE_B200_H */

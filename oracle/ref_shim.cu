@@ -1,0 +1,58 @@
+// extern "C" shim around the reference's own GPU launchers, so the parity tests can call the
+// reference kernels (compiled for sm_100a from their sources, unmodified) through ctypes.
+// TEST INFRASTRUCTURE: built by oracle/build.py into oracle/_ref/libforge_ref.so, only when
+// the reference source tree is present; loaded only by tests/ and bench.py's comparison legs.
+#include <forge/gemm/int8_dense.cuh>
+#include <forge/gemm/int8_sparse.cuh>
+#include <forge/quant/dequantize.cuh>
+#include <forge/quant/quantize.cuh>
+#include <forge/sparsity/pack_metadata.cuh>
+#include <forge/sparsity/prune_compress.cuh>
+
+extern "C" {
+
+void ref_fused_quantize_activation(const void* in, int8_t* out, float* scales, int M, int K, void* stream) {
+    forge::quant::fused_quantize_activation((const __half*)in, out, scales, M, K, (cudaStream_t)stream);
+}
+// the two-pass kernel launched directly, as tests/test_quantize.cu:54-55 does
+void ref_quantize_two_pass(const void* in, int8_t* out, float* scales, int M, int K, void* stream) {
+    int threads = ((K + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    forge::quant::fused_quantize_activation_kernel<<<M, threads, 0, (cudaStream_t)stream>>>((const __half*)in, out,
+                                                                                            scales, K);
+}
+void ref_fused_dequantize_bias(const int32_t* in, const float* as, const void* ws, const void* bias, void* out, int M,
+                               int N, void* stream) {
+    forge::quant::fused_dequantize_bias(in, as, (const __half*)ws, (const __half*)bias, (__half*)out, M, N,
+                                        (cudaStream_t)stream);
+}
+void ref_int8_gemm_dequant(const int8_t* A, const int8_t* B, const float* as, const void* ws, const void* bias,
+                           void* out, int M, int K, int N, void* stream) {
+    forge::gemm::int8_gemm_dequant(A, B, as, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N,
+                                   (cudaStream_t)stream);
+}
+void ref_int8_linear(const void* x, const int8_t* w, const void* ws, const void* bias, void* out, int M, int K, int N,
+                     int8_t* sa, float* ss, void* stream) {
+    forge::gemm::int8_linear((const __half*)x, w, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N, sa,
+                             ss, (cudaStream_t)stream);
+}
+void ref_sparse_int8_gemm(const int8_t* Wc, const int8_t* x, const uint32_t* meta, const float* as, const void* ws,
+                          const void* bias, void* out, int M, int K, int N, float* wksp, int split_k, void* stream,
+                          int tile) {
+    forge::gemm::sparse_int8_gemm(Wc, x, meta, as, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N,
+                                  wksp, split_k, (cudaStream_t)stream, tile);
+}
+void ref_sparse_int8_linear(const void* x, const int8_t* Wc, const uint32_t* meta, const void* ws, const void* bias,
+                            void* out, int M, int K, int N, int8_t* sx, float* ss, float* wksp, int split_k,
+                            void* stream, int path) {
+    forge::gemm::sparse_int8_linear((const __half*)x, Wc, meta, (const __half*)ws, (const __half*)bias, (__half*)out,
+                                    M, K, N, sx, ss, wksp, split_k, (cudaStream_t)stream, path);
+}
+void ref_prune_compress_24(const int8_t* w, int8_t* c, uint8_t* m, int N, int K, void* stream) {
+    forge::sparsity::prune_compress_24(w, c, m, N, K, (cudaStream_t)stream);
+}
+void ref_pack_metadata(const uint8_t* raw, uint32_t* packed, int N, int K, void* stream) {
+    forge::sparsity::pack_metadata(raw, packed, N, K, (cudaStream_t)stream);
+}
+
+}  // extern "C"

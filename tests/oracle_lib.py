@@ -1,0 +1,198 @@
+"""ctypes access to the test oracles: oracle/liboracle.so (CPU restatement, numpy in/out) and
+oracle/_ref/libforge_ref.so (the reference's own CUDA kernels built for sm_100a, torch CUDA
+tensors in/out). Test infrastructure only."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+ORACLE_SO = os.path.join(ROOT, "oracle", "liboracle.so")
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libforge_ref.so")
+
+_vp, _i = ctypes.c_void_p, ctypes.c_int
+_oracle = None
+_ref = None
+
+
+def oracle():
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_SO):
+            sys.path.insert(0, os.path.join(ROOT, "oracle"))
+            import build as oracle_build  # noqa: E402
+            oracle_build.build_oracle()
+        lib = ctypes.CDLL(ORACLE_SO)
+        lib.oracle_int8_gemm_s32.argtypes = [_vp, _vp, _vp, _i, _i, _i]
+        lib.oracle_quantize.argtypes = [_vp, _vp, _vp, _i, _i]
+        lib.oracle_dequantize_bias.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i]
+        lib.oracle_dequantize_gemm_epilogue.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i]
+        lib.oracle_prune_compress_24.argtypes = [_vp, _vp, _vp, _i, _i]
+        lib.oracle_prune_24_dense.argtypes = [_vp, _vp, _i, _i]
+        lib.oracle_pack_metadata.argtypes = [_vp, _vp, _i, _i]
+        lib.oracle_sparse_gemm_s32.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i]
+        lib.oracle_float_to_half.argtypes = [ctypes.c_float]
+        lib.oracle_float_to_half.restype = ctypes.c_uint16
+        lib.oracle_half_to_float.argtypes = [ctypes.c_uint16]
+        lib.oracle_half_to_float.restype = ctypes.c_float
+        lib.oracle_num_threads.restype = _i
+        _oracle = lib
+    return _oracle
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data
+
+
+def _c(a, dtype):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == dtype, (a.dtype, dtype)
+    return a
+
+
+def gemm_s32(A, B):
+    A, B = _c(A, np.int8), _c(B, np.int8)
+    M, K = A.shape
+    N = B.shape[0]
+    C = np.empty((M, N), np.int32)
+    oracle().oracle_int8_gemm_s32(_p(A), _p(B), _p(C), M, K, N)
+    return C
+
+
+def quantize(x_f16):
+    x = _c(x_f16, np.float16)
+    M, K = x.shape
+    q = np.empty((M, K), np.int8)
+    s = np.empty((M,), np.float32)
+    oracle().oracle_quantize(_p(x), _p(q), _p(s), M, K)
+    return q, s
+
+
+def dequantize_bias(acc, act_scale, w_scale, bias, gemm_epilogue=False):
+    acc, act_scale, w_scale = _c(acc, np.int32), _c(act_scale, np.float32), _c(w_scale, np.float16)
+    bias = None if bias is None else _c(bias, np.float16)
+    M, N = acc.shape
+    out = np.empty((M, N), np.float16)
+    fn = oracle().oracle_dequantize_gemm_epilogue if gemm_epilogue else oracle().oracle_dequantize_bias
+    fn(_p(acc), _p(act_scale), _p(w_scale), _p(bias), _p(out), M, N)
+    return out
+
+
+def prune_compress_24(w):
+    w = _c(w, np.int8)
+    N, K = w.shape
+    comp = np.empty((N, K // 2), np.int8)
+    meta = np.empty((N * (K // 4),), np.uint8)
+    oracle().oracle_prune_compress_24(_p(w), _p(comp), _p(meta), N, K)
+    return comp, meta
+
+
+def prune_24_dense(w):
+    w = _c(w, np.int8)
+    N, K = w.shape
+    out = np.empty((N, K), np.int8)
+    oracle().oracle_prune_24_dense(_p(w), _p(out), N, K)
+    return out
+
+
+def pack_metadata(meta_raw, N, K):
+    meta_raw = _c(meta_raw, np.uint8)
+    out = np.empty((N, K // 32), np.uint32)
+    oracle().oracle_pack_metadata(_p(meta_raw), _p(out), N, K)
+    return out
+
+
+def sparse_gemm_s32(W_comp, x, w_meta):
+    W_comp, x, w_meta = _c(W_comp, np.int8), _c(x, np.int8), _c(w_meta, np.uint32)
+    M, K = x.shape
+    N = W_comp.shape[0]
+    out = np.empty((M, N), np.int32)
+    oracle().oracle_sparse_gemm_s32(_p(W_comp), _p(x), _p(w_meta), _p(out), M, K, N)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# Reference GPU kernels (oracle/_ref). Arguments are torch CUDA tensors.
+
+def ref_available():
+    return os.path.exists(REF_SO)
+
+
+def ref():
+    global _ref
+    if _ref is None:
+        lib = ctypes.CDLL(REF_SO)
+        lib.ref_fused_quantize_activation.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        lib.ref_quantize_two_pass.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        lib.ref_fused_dequantize_bias.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]
+        lib.ref_int8_gemm_dequant.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        lib.ref_int8_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]
+        lib.ref_sparse_int8_gemm.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _i]
+        lib.ref_sparse_int8_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i]
+        lib.ref_prune_compress_24.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        lib.ref_pack_metadata.argtypes = [_vp, _vp, _i, _i, _vp]
+        for name in ("ref_fused_quantize_activation", "ref_quantize_two_pass", "ref_fused_dequantize_bias",
+                     "ref_int8_gemm_dequant", "ref_int8_linear", "ref_sparse_int8_gemm", "ref_sparse_int8_linear",
+                     "ref_prune_compress_24", "ref_pack_metadata"):
+            getattr(lib, name).restype = None
+        _ref = lib
+    return _ref
+
+
+def tp(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def cur_stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ref_quantize(x, two_pass=False):
+    import torch
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    fn = ref().ref_quantize_two_pass if two_pass else ref().ref_fused_quantize_activation
+    fn(tp(x), tp(q), tp(s), M, K, cur_stream())
+    return q, s
+
+
+def ref_dequantize_bias(acc, act_scale, w_scale, bias):
+    import torch
+    M, N = acc.shape
+    out = torch.empty((M, N), dtype=torch.float16, device=acc.device)
+    ref().ref_fused_dequantize_bias(tp(acc), tp(act_scale), tp(w_scale), tp(bias), tp(out), M, N, cur_stream())
+    return out
+
+
+def ref_int8_gemm_dequant(A, B, act_scale, w_scale, bias):
+    import torch
+    M, K = A.shape
+    N = B.shape[0]
+    out = torch.empty((M, N), dtype=torch.float16, device=A.device)
+    ref().ref_int8_gemm_dequant(tp(A), tp(B), tp(act_scale), tp(w_scale), tp(bias), tp(out), M, K, N, cur_stream())
+    return out
+
+
+def ref_sparse_int8_gemm(W_comp, x, w_meta, act_scale, w_scale, bias, tile=-1):
+    import torch
+    M, K = x.shape
+    N = W_comp.shape[0]
+    out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    ref().ref_sparse_int8_gemm(tp(W_comp), tp(x), tp(w_meta), tp(act_scale), tp(w_scale), tp(bias), tp(out), M, K, N,
+                               0, 1, cur_stream(), tile)
+    return out
+
+
+def ref_prune_pack(w):
+    import torch
+    N, K = w.shape
+    comp = torch.empty((N, K // 2), dtype=torch.int8, device=w.device)
+    raw = torch.empty((N * (K // 4),), dtype=torch.uint8, device=w.device)
+    packed = torch.empty((N, K // 32), dtype=torch.int32, device=w.device)
+    ref().ref_prune_compress_24(tp(w), tp(comp), tp(raw), N, K, cur_stream())
+    ref().ref_pack_metadata(tp(raw), tp(packed), N, K, cur_stream())
+    return comp, raw, packed
