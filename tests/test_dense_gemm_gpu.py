@@ -40,8 +40,9 @@ def _status_ok():
 @pytest.mark.parametrize("M,K,N", SHAPES)
 def test_s32_bit_exact(M, K, N):
     A, B, *_ = _inputs(M, K, N, 1234 + M + K + N)
-    out = torch.full((M, N), 0x7B7B7B7B, dtype=torch.int32, device=DEV)
-    _lib.call("forge_int8_gemm_s32", A.to(DEV).data_ptr(), B.to(DEV).data_ptr(), out.data_ptr(), M, K, N, 0)
+    out = torch.full((M, N), 0x7B7B7B7B, dtype=torch.int32, device=DEV)   # garbage: must be overwritten
+    dA, dB = A.to(DEV), B.to(DEV)
+    _lib.call("forge_int8_gemm_s32", dA.data_ptr(), dB.data_ptr(), out.data_ptr(), M, K, N, 0)
     _status_ok()
     assert np.array_equal(out.cpu().numpy(), O.gemm_s32(A.numpy(), B.numpy()))
 
@@ -122,7 +123,8 @@ def test_int8_linear_matches_quantize_then_gemm():
     if O.ref_available():
         ref = torch.empty_like(out)
         sa2, ss2 = torch.empty_like(sa), torch.empty_like(ss)
-        O.ref().ref_int8_linear(x.data_ptr(), B.to(DEV).data_ptr(), w_s.to(DEV).data_ptr(), bias.to(DEV).data_ptr(),
+        dB, dws, dbias = B.to(DEV), w_s.to(DEV), bias.to(DEV)
+        O.ref().ref_int8_linear(x.data_ptr(), dB.data_ptr(), dws.data_ptr(), dbias.data_ptr(),
                                 ref.data_ptr(), M, K, N, sa2.data_ptr(), ss2.data_ptr(), O.cur_stream())
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16))

@@ -45,7 +45,8 @@ def _status_ok():
 def test_s32_equals_dense_gemm_on_pruned_weights(M, K, N):
     W, x, _, _, _, comp, packed = _prep(M, K, N, 42 + M + K + N)
     out = torch.full((M, N), 0x7B7B7B7B, dtype=torch.int32, device=DEV)
-    _lib.call("forge_sparse_int8_gemm_s32", comp.data_ptr(), x.to(DEV).data_ptr(), packed.data_ptr(), out.data_ptr(),
+    dx = x.to(DEV)
+    _lib.call("forge_sparse_int8_gemm_s32", comp.data_ptr(), dx.data_ptr(), packed.data_ptr(), out.data_ptr(),
               M, K, N, 0)
     _status_ok()
     want = O.gemm_s32(x.numpy(), O.prune_24_dense(W.numpy()))
