@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the forge_b200 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (every N): the headline of the metric, the dense INT8 GEMM with fused dequant + bias
+at M = N = K = 8192 per GPU (forge::gemm::int8_gemm_dequant), int8 operands uniform in
+[-127,127] from seeded Philox streams. A "step" is one call on one batch of activations.
+  value : whole-job INT8 TOPS (2*M*N*K per step per GPU) with inputs resident in HBM.
+  e2e   : the same call through the C ABI with HOST buffers: the step's activations and
+          their scales are copied from pinned host memory and the FP16 result is copied back,
+          inside the timed region (three streams, copies overlapped with the kernel).
+With N > 1 (torchrun, one rank per GPU) token rows are sharded: every rank runs the same
+per-GPU workload on its own rows, no collective on the data path ("weak" scaling).
+
+--impl reference times the reference's host int32 GEMM + dequant loop (the CPU restatement in
+oracle/, all host threads) on a bounded row sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+OPS_PER_STEP = 2.0 * M * N * K
+METRIC = "int8_gemm_dequant_tops_m8192_n8192_k8192"
+UNIT = "TOPS"
+CPU_SAMPLE_ROWS = 256
+# dram__bytes_read.sum + dram__bytes_write.sum of one dense_gemm_kernel<256,1> launch at 8192^3
+# (single-pass ncu capture of this workload; see profiles/). None until measured.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"], "hbm": p["hbm_gbs"],
+                "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons through NVML (read-only) while `active` is set."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.active = threading.Event()
+        self._halt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+                getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            }
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._halt.is_set():
+                if self.active.is_set():
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    r = get_reasons(h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                time.sleep(0.02)
+        except Exception as e:  # clocks are evidence, not the product: report the failure, keep benchmarking
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._halt.set()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(self.samples), "reasons": sorted(self.reasons)}
+
+
+def _cpu_baseline(rows, reps):
+    """Reference host loop (int32 GEMM + dequant) on `rows` token rows of the workload."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as O
+    rng = np.random.default_rng(1234)
+    A = rng.integers(-127, 128, (rows, K), dtype=np.int8)
+    B = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    a_s = rng.random(rows, dtype=np.float32) * 0.05
+    w_s = (rng.random(N, dtype=np.float32) * 0.05).astype(np.float16)
+    bias = (rng.random(N, dtype=np.float32) - 0.5).astype(np.float16)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        acc = O.gemm_s32(A, B)
+        O.dequantize_bias(acc, a_s, w_s, bias, gemm_epilogue=True)
+        times.append(time.perf_counter() - t0)
+    return times, O.oracle().oracle_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # size the per-step row sample so that warmup + steps take about a minute of host time
+    probe, _ = _cpu_baseline(8, 2)
+    rows_per_s = 8 / min(probe)
+    rows = int(max(1, min(CPU_SAMPLE_ROWS, rows_per_s * 60.0 / (args.warmup + args.steps))))
+    times, cores = _cpu_baseline(rows, args.warmup + args.steps)
+    timed = times[args.warmup:]
+    total = sum(timed)
+    tops = 2.0 * rows * N * K * len(timed) / total / 1e12
+    sample = f"{rows} of {M} token rows per step (int32 GEMM + dequant host loop, OpenMP)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(timed), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+        "config": {"workload": "int8_gemm_dequant M=N=K=8192 (host reference loop on a row sample)",
+                   "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from forge_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()   # raises if libforge_b200.so is missing: there is no fallback
+
+    NSETS = 3   # activation/output buffer sets rotated between steps: 256 MiB touched per step > 126 MB L2
+    g = torch.Generator(device=dev)
+    g.manual_seed(1235)
+    B = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8, device=dev)
+    w_s = (torch.rand(N, generator=g, device=dev) * 0.02 + 0.001).to(torch.float16)
+    bias = (torch.randn(N, generator=g, device=dev) * 0.01).to(torch.float16)
+    A, a_s, out = [], [], []
+    for i in range(NSETS):
+        g.manual_seed(1234 + 100 * rank + i)
+        A.append(torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8, device=dev))
+        a_s.append(torch.rand(M, generator=g, device=dev) * 0.05 + 0.001)
+        out.append(torch.empty((M, N), dtype=torch.float16, device=dev))
+    stream = torch.cuda.current_stream()
+
+    def step(i, s=None):
+        j = i % NSETS
+        st = lib.forge_int8_gemm_dequant(A[j].data_ptr(), B.data_ptr(), a_s[j].data_ptr(), w_s.data_ptr(),
+                                         bias.data_ptr(), out[j].data_ptr(), M, K, N,
+                                         (s or stream).cuda_stream)
+        if st != 0:
+            raise RuntimeError(f"forge_int8_gemm_dequant returned {st}")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    # ---- device-resident throughput
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.active.set()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    sampler.active.clear()
+    ms = e0.elapsed_time(e1)
+    if lib.forge_b200_device_status(1) != 0:
+        raise RuntimeError("a forge_b200 kernel gave up on a bounded wait")
+
+    # ---- end to end: host buffers in, host buffers out, every step
+    hA = [torch.randint(-127, 128, (M, K), dtype=torch.int8).pin_memory() for _ in range(2)]
+    h_as = [torch.rand(M).pin_memory() for _ in range(2)]
+    h_out = [torch.empty((M, N), dtype=torch.float16).pin_memory() for _ in range(2)]
+    s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(NSETS)]
+    ev_run = [torch.cuda.Event() for _ in range(NSETS)]
+    ev_out = [torch.cuda.Event() for _ in range(NSETS)]
+
+    def e2e_loop(n):
+        for i in range(n):
+            j = i % NSETS
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_run[j])          # the kernel that last read this set is done
+                A[j].copy_(hA[i % 2], non_blocking=True)
+                a_s[j].copy_(h_as[i % 2], non_blocking=True)
+                ev_in[j].record(s_in)
+            s_run.wait_event(ev_in[j])
+            s_run.wait_event(ev_out[j])             # the copy-out that last read this output is done
+            step(i, s_run)
+            ev_run[j].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[j])
+                h_out[i % 2].copy_(out[j], non_blocking=True)
+                ev_out[j].record(s_out)
+
+    e2e_warm = min(args.warmup, 5)
+    e2e_steps = min(args.steps, 200)   # each step moves 192 MiB over PCIe; bounded so defaults stay in minutes
+    e2e_loop(e2e_warm)
+    barrier()
+    t0 = time.perf_counter()
+    e2 = torch.cuda.Event(enable_timing=True)
+    e3 = torch.cuda.Event(enable_timing=True)
+    e2.record(s_in)
+    e2e_loop(e2e_steps)
+    s_out.synchronize()
+    e3.record(s_out)
+    barrier()
+    e2e_ms = e2.elapsed_time(e3)
+    _ = t0
+    sampler.stop()
+
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value = OPS_PER_STEP * args.steps * world / (ms * 1e-3) / 1e12
+    e2e_value = OPS_PER_STEP * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+    peaks = _peaks()
+    launch_ms = ms / args.steps
+    sustained = ms > 250.0
+    peak_bf16 = peaks["bf16_sustained"] if sustained else peaks["bf16_burst"]
+    achieved = OPS_PER_STEP / (launch_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": 2.0 * peak_bf16, "unit": "TOP/s",
+        "frac": achieved / (2.0 * peak_bf16), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+        "kernel": "dense_gemm_kernel<256,1> (tcgen05.mma kind::i8, 128x256 tiles)",
+        "peak_basis": f"2 x {'sustained' if sustained else 'burst'} cuBLAS bf16 TFLOP/s of {peaks['source']} "
+                      "(kind::i8 issues at twice the bf16 rate); nominal dense int8 is 4500",
+        "frac_of_nominal_4500": achieved / 4500.0,
+    }
+    cpu = None
+    if world == 1:
+        times_cpu, cores = _cpu_baseline(CPU_SAMPLE_ROWS, 3)
+        best = min(times_cpu)
+        cpu = {"value": 2.0 * CPU_SAMPLE_ROWS * N * K / best / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{CPU_SAMPLE_ROWS} of {M} token rows, best of 3 (int32 GEMM + dequant host loop, OpenMP)"}
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": launch_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
+        "data": "synthetic",
+        "config": {"workload": "int8_gemm_dequant M=N=K=8192 per GPU (headline shape of the metric)",
+                   "operands": "int8 uniform [-127,127], seeded Philox; fp32 token scales, fp16 channel scales + bias",
+                   "sharding": "token rows, one shard per GPU, no collective" if world > 1 else "single GPU",
+                   "l2": f"{NSETS} rotating activation/output buffer sets, 256 MiB touched per step (L2 is 126 MB)"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M * K + 4 * M, "d2h_bytes_per_step": 2 * M * N,
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "note": "weights resident; activations+scales copied in and FP16 result copied out every step"},
+        "gpu_launches": args.steps,
+        "clocks": sampler.summary(),
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+    }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_case(args):
+    """Single-kernel timing cases (also the commands the ncu summaries under profiles/ were made
+    with). Prints one JSON line: kernel time from CUDA events, achieved rate, roofline fraction."""
+    import torch
+    from forge_b200 import _forge_C as C
+    from forge_b200 import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    peaks = _peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    name = args.case
+    s = torch.cuda.current_stream().cuda_stream
+
+    def ri8(*shape):
+        return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev)
+
+    work, unit, bound = None, None, None
+    if name in ("dense", "dense_s32", "sparse", "sparse_s32"):
+        m, n, k = args.m or 8192, args.n or 8192, args.k or 8192
+        a_s = torch.rand(m, generator=g, device=dev) * 0.05 + 0.001
+        w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
+        bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
+        x, W = ri8(m, k), ri8(n, k)
+        out = torch.empty((m, n), dtype=torch.int32 if name.endswith("s32") else torch.float16, device=dev)
+        work, unit, bound = 2.0 * m * n * k / 1e12, "TOP/s", "tensor"
+        if name.startswith("sparse"):
+            comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+            raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+            meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+            C.prune_compress_24(W, comp, raw, n, k)
+            C.pack_metadata(raw, meta, n, k)
+            if name == "sparse":
+                fn = lambda: lib.forge_sparse_int8_gemm(comp.data_ptr(), x.data_ptr(), meta.data_ptr(), a_s.data_ptr(),
+                                                        w_s.data_ptr(), bias.data_ptr(), out.data_ptr(), m, k, n, 0, 1,
+                                                        s, -1)
+            else:
+                fn = lambda: lib.forge_sparse_int8_gemm_s32(comp.data_ptr(), x.data_ptr(), meta.data_ptr(),
+                                                            out.data_ptr(), m, k, n, s)
+        elif name == "dense":
+            fn = lambda: lib.forge_int8_gemm_dequant(x.data_ptr(), W.data_ptr(), a_s.data_ptr(), w_s.data_ptr(),
+                                                     bias.data_ptr(), out.data_ptr(), m, k, n, s)
+        else:
+            fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, s)
+        shape = {"M": m, "N": n, "K": k}
+    elif name == "quantize":
+        m, k = args.m or 16384, args.k or 8192
+        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
+        q = torch.empty((m, k), dtype=torch.int8, device=dev)
+        sc = torch.empty((m,), dtype=torch.float32, device=dev)
+        fn = lambda: lib.forge_fused_quantize_activation(x.data_ptr(), q.data_ptr(), sc.data_ptr(), m, k, s)
+        work, unit, bound, shape = (3.0 * m * k + 4.0 * m) / 1e9, "GB/s", "hbm", {"M": m, "K": k}
+    elif name == "dequant":
+        m, n = args.m or 8192, args.n or 8192
+        acc = torch.randint(-50000, 50000, (m, n), generator=g, dtype=torch.int32, device=dev)
+        a_s = torch.rand(m, generator=g, device=dev)
+        w_s = torch.rand(n, generator=g, device=dev).half()
+        bias = torch.rand(n, generator=g, device=dev).half()
+        out = torch.empty((m, n), dtype=torch.float16, device=dev)
+        fn = lambda: lib.forge_fused_dequantize_bias(acc.data_ptr(), a_s.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
+                                                     out.data_ptr(), m, n, s)
+        work, unit, bound, shape = (6.0 * m * n + 4.0 * m + 4.0 * n) / 1e9, "GB/s", "hbm", {"M": m, "N": n}
+    elif name in ("prune", "pack"):
+        n, k = args.n or 28672, args.k or 8192
+        W = ri8(n, k)
+        comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+        raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+        meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+        C.prune_compress_24(W, comp, raw, n, k)
+        if name == "prune":
+            fn = lambda: lib.forge_prune_compress_24(W.data_ptr(), comp.data_ptr(), raw.data_ptr(), n, k, s)
+            work = 1.75 * n * k / 1e9
+        else:
+            fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, s)
+            work = 0.375 * n * k / 1e9
+        unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
+    else:
+        raise SystemExit(f"unknown case {name}")
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.flush_l2 else None
+    for _ in range(args.warmup):
+        assert fn() == 0
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        assert fn() == 0
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    assert lib.forge_b200_device_status(1) == 0
+    ms = statistics.median(times)
+    achieved = work / (ms * 1e-3)
+    peak = 2.0 * peaks["bf16_burst"] if bound == "tensor" else peaks["hbm"]
+    print(json.dumps({"case": name, "shape": shape, "ms": ms, "ms_min": min(times), "achieved": achieved, "unit": unit,
+                      "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
+                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default="headline",
+                    help="headline (the contract line) or one kernel: dense, dense_s32, sparse, sparse_s32, "
+                         "quantize, dequant, prune, pack")
+    ap.add_argument("--m", type=int, default=0)
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")
+    args = ap.parse_args()
+    if args.case != "headline":
+        run_case(args)
+        return
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
