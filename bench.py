@@ -33,8 +33,8 @@ METRIC = "int8_gemm_dequant_tops_m8192_n8192_k8192"
 UNIT = "TOPS"
 CPU_SAMPLE_ROWS = 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one dense_gemm_kernel<256,1> launch at 8192^3
-# (single-pass ncu capture of this workload; see profiles/). None until measured.
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# (profiles/dense_gemm_kernel_8192.md: 333.1 MB read + 114.4 MB written).
+NCU_DRAM_BYTES_PER_LAUNCH = 447.5e6
 
 
 def _peaks():

@@ -47,3 +47,18 @@ def test_public_kernel_symbols_are_exported():
     for frag in ("fused_quantize_activation_kernel", "fused_dequantize_bias_kernel", "prune_compress_kernel",
                  "pack_metadata_kernel"):
         assert frag in out
+
+
+def test_cxx_face_compiles_and_links(tmp_path):
+    """Reference-style C++ (namespaces, defaults, public kernels launched with <<<>>>) builds
+    against include/forge/... and links against libforge_b200.so."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = str(tmp_path / "dropin")
+    cmd = [nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "cxx_dropin_check.cu"), "-o", exe, "-L" + os.path.dirname(_lib.LIB_PATH),
+           "-lforge_b200", "-Xlinker", "-rpath=" + os.path.dirname(_lib.LIB_PATH)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert subprocess.run([exe]).returncode == 0
