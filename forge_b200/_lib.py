@@ -22,6 +22,7 @@ SIGNATURES = {
     "forge_int8_dp4a_gemm_dequant": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "forge_int8_linear": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
     "forge_int8_dp4a_linear": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
+    "forge_int8_linear_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "forge_get_compute_capability": [_i],
     "forge_has_wmma_int8": [_i],
     "forge_int8_gemm_s32": [_vp, _vp, _vp, _i, _i, _i, _vp],

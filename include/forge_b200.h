@@ -83,6 +83,18 @@ int forge_has_wmma_int8(int device);
 int forge_int8_gemm_s32(const int8_t* A, const int8_t* B, int32_t* output, int M, int K, int N,
                         forge_stream_t stream);
 
+/* No counterpart in the reference. forge_int8_linear for callers that cannot provide the two
+ * scratch buffers: code that runs where device allocation is off-limits (a plug-in under a host
+ * framework whose allocator owns the GPU's memory, a serving loop that must not hit cudaMalloc's
+ * device-wide synchronisation). The scratch lives in a fixed 16 MiB + 64 KiB array inside the
+ * library image (resident in every context that loads the library until exit); the call
+ * allocates nothing. Limits: M*K <= 16777216 and M <= 16384, otherwise FORGE_B200_TOO_LARGE.
+ * All calls on a device share the array, so calls that may overlap on the GPU race - order
+ * them. The first call on a device resolves the array's address; make it at start-up, before
+ * any stream capture. Output is bit-identical to forge_int8_linear. */
+int forge_int8_linear_static(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias,
+                             void* output, int M, int K, int N, forge_stream_t stream);
+
 /* ---------------------------------------------------------------- forge::gemm, 2:4 sparse */
 
 /* Tile / path ids of include/forge/gemm/int8_sparse.cuh:26-31,74-76. */
