@@ -17,11 +17,12 @@ inline cudaStream_t S(forge_stream_t s) { return reinterpret_cast<cudaStream_t>(
 inline const __half* H(const void* p) { return static_cast<const __half*>(p); }
 inline __half* H(void* p) { return static_cast<__half*>(p); }
 
-// Tile id of the reference API -> token-tile width of the tcgen05 kernel. Weight tiles are
-// always 128 rows here; the reference's 256-row tile maps to the widest token tile.
+// Tile id of the reference API -> tile knob of the tcgen05 kernels: the reference's 256-row
+// weight tile is the CTA-pair kernel (256 weight rows x 224 tokens per pair, knob 1000 + 224);
+// its 128-row tiles are the single-CTA kernel with 128 / 64 tokens.
 inline int tile_to_bt(int tile) {
     switch (tile) {
-    case FORGE_SPARSE_TILE_256x128: return 128;
+    case FORGE_SPARSE_TILE_256x128: return 1224;
     case FORGE_SPARSE_TILE_128x128: return 128;
     case FORGE_SPARSE_TILE_128x64: return 64;
     default: return 0;
@@ -103,10 +104,12 @@ int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_w
     if (tile >= FORGE_SPARSE_NUM_TILES) tile = FORGE_SPARSE_TILE_AUTO;
     int t = tile;
     if (t < 0) {
-        // automatic: 128-token tiles once they give every SM work, else 64-token tiles
+        // automatic: the CTA-pair kernel for large problems, else 128-token tiles once they give
+        // every SM work, else 64-token tiles (mirrors sparse_dispatch in gemm_sparse.cu)
         const long long w_blocks = (N_out + 127) / 128;
-        t = (M > 64 && w_blocks * ((M + 127) / 128) >= sm_count()) ? FORGE_SPARSE_TILE_128x128
-                                                                    : FORGE_SPARSE_TILE_128x64;
+        if (M >= 1024 && N_out >= 512) t = FORGE_SPARSE_TILE_256x128;
+        else t = (M > 64 && w_blocks * ((M + 127) / 128) >= sm_count()) ? FORGE_SPARSE_TILE_128x128
+                                                                         : FORGE_SPARSE_TILE_128x64;
     }
     // The K loop is never split: the exact s32 accumulation in TMEM covers the whole K range.
     (void)split_k;

@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "gemm_dense.cuh"
+#include "gemm_pair.cuh"
 
 namespace fb200 {
 
@@ -389,6 +390,13 @@ int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, con
         dense_gemm_ragged_kernel<EPI><<<(unsigned)grid, block, 0, stream>>>(A, B, act_scale, w_scale, bias, out, M,
                                                                            N, K);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+    // 512: the CTA-pair kernel (256 x 256 outputs per pair of SMs).
+    if (force_bn == 512) {
+        const int r = (EPI == 0) ? dense_pair_s32(A, B, static_cast<int32_t*>(out), M, K, N, stream)
+                                 : dense_pair_dequant(A, B, act_scale, w_scale, bias, static_cast<__half*>(out), M,
+                                                      K, N, stream);
+        if (r >= 0) return r;
     }
     // Tile width: the widest tile that still gives every SM work.
     int bn = force_bn;

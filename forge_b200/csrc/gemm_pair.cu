@@ -1,0 +1,691 @@
+// CTA-pair (tcgen05 cta_group::2) variants of the dense and 2:4-sparse INT8 GEMMs.
+//
+// Two CTAs on neighbouring SMs form a cluster and share one UMMA tile: the dense kernel
+// computes 256 x 256 outputs per pair, the sparse kernel 256 weight rows x BT tokens. Each CTA
+// stages only its own half of BOTH operands (128 rows of the M-side operand, N/2 rows of the
+// N-side operand) in its shared memory with ordinary TMA loads - no cluster multicast - and
+// the leader CTA's single MMA thread issues tcgen05.mma.cta_group::2, which reads both CTAs'
+// shared memory and writes both CTAs' tensor memory. Per output this halves the N-side operand
+// bytes a CTA has to pull from L2, which is what limits the single-CTA kernels.
+//
+// Barrier protocol (per pipeline stage s; "leader" = cluster rank 0):
+//   full[s]   lives in the leader. The leader's producer arms it with the byte count of both
+//             CTAs' loads; every TMA load of either CTA reports its bytes to it.
+//   empty[s]  one per CTA. The leader's MMA thread commits to both after the MMAs that read
+//             stage s, each CTA's producer waits on its own.
+//   tmem_full[b]  one per CTA, committed by the leader after a tile's last MMA.
+//   tmem_empty[b] lives in the leader; the 4 + 4 epilogue warps of both CTAs arrive on it.
+// Every wait is bounded; a wait that runs out sets the CTA's abort flag and the device status
+// word, and all roles fall through to the common teardown (cluster barrier, TMEM free).
+#include "common.cuh"
+#include "ptx.cuh"
+#include "gemm_dense.cuh"
+#include "gemm_pair.cuh"
+#include "sparse_epilogue.cuh"
+
+namespace fb200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kEpiThreads = 128;
+constexpr int kSpEpiWarps = 8;            // sparse kernel: two warps per TMEM lane quarter
+constexpr int kSpThreads = 64 + 32 * kSpEpiWarps;
+
+// Shared bookkeeping at the tail of dynamic shared memory.
+struct PairBars {
+    uint64_t* full;        // [stages], used in the leader
+    uint64_t* empty;       // [stages]
+    uint64_t* tmem_full;   // [2]
+    uint64_t* tmem_empty;  // [2], used in the leader
+    uint32_t* tmem_slot;
+    volatile int* abort_flag;
+};
+
+__device__ __forceinline__ PairBars carve_bars(uint8_t* p, int stages) {
+    PairBars b;
+    uint64_t* q = reinterpret_cast<uint64_t*>(p);
+    b.full = q;
+    b.empty = q + stages;
+    b.tmem_full = q + 2 * stages;
+    b.tmem_empty = b.tmem_full + 2;
+    b.tmem_slot = reinterpret_cast<uint32_t*>(b.tmem_empty + 2);
+    b.abort_flag = reinterpret_cast<volatile int*>(b.tmem_slot + 1);
+    return b;
+}
+
+__device__ __forceinline__ void init_bars(const PairBars& b, int stages, int epi_warps) {
+    for (int s = 0; s < stages; s++) {
+        mbar_init(&b.full[s], 1);
+        mbar_init(&b.empty[s], 1);
+    }
+    for (int i = 0; i < 2; i++) {
+        mbar_init(&b.tmem_full[i], 1);
+        mbar_init(&b.tmem_empty[i], 2 * epi_warps);
+    }
+    *b.abort_flag = 0;
+    fence_mbar_init();
+}
+
+struct TileCoord {
+    int a_blk, b_blk;   // block index along the M-side operand / the N-side operand
+};
+
+// Bands of `group` blocks of the M-side operand, N-side block major inside a band.
+__device__ __forceinline__ TileCoord tile_coord(int t, int a_blocks, int b_blocks, int group) {
+    const int band_tiles = group * b_blocks;
+    const int band = t / band_tiles;
+    const int first = band * group;
+    const int rows = min(group, a_blocks - first);
+    const int r = t - band * band_tiles;
+    TileCoord c;
+    c.a_blk = first + r % rows;
+    c.b_blk = r / rows;
+    return c;
+}
+
+// ============================================================================================
+// Dense: 256 x 256 outputs per pair. CTA r holds A rows [128r, 128r+128) and B rows
+// [128r, 128r+128) of the tile; its TMEM receives output rows [128r, 128r+128) x 256 columns.
+
+struct DensePairCfg {
+    static constexpr int kStages = 6;
+    static constexpr int kABytes = 128 * 128;
+    static constexpr int kBBytes = 128 * 128;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kEpiBufs = 2;
+    static constexpr int kEpiBufBytes = 32 * 128;
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
+    static constexpr int kScaleBytes = 2 * 256 * 2 * (int)sizeof(__half);
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kScaleBytes + kBarBytes;
+    static constexpr int kTmemCols = 512;
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory limit");
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ act_scale,
+                  const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
+                  int* __restrict__ status) {
+    using Cfg = DensePairCfg;
+    constexpr int BN = 256;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* smem_ab = smem;
+    uint8_t* smem_epi = smem + Cfg::kStages * Cfg::kStageBytes;
+    __half* smem_scale = reinterpret_cast<__half*>(smem_epi + Cfg::kEpiBytes);
+    const PairBars bars = carve_bars(smem_epi + Cfg::kEpiBytes + Cfg::kScaleBytes, Cfg::kStages);
+
+    const int warp_id = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = (rank == 0);
+    const bool aligned = (smem_u32(smem) & 1023u) == 0;   // same in both CTAs of the pair
+    if (!aligned) {
+        if (threadIdx.x == 0) atomicExch(status, 300);
+        return;
+    }
+
+    const int m_blocks = (M + 255) / 256;
+    const int n_blocks = (N + 255) / 256;
+    const int num_tiles = m_blocks * n_blocks;
+    const int num_kb = (K + 127) / 128;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) init_bars(bars, Cfg::kStages, kEpiWarps);
+    if (warp_id == 0 && lane == 0) {
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_c);
+    }
+    if (warp_id == 1) {
+        tmem_alloc_pair(bars.tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *bars.tmem_slot;
+
+    if (warp_id == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+                const TileCoord tc = tile_coord(t, m_blocks, n_blocks, 8);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
+                        atomicExch(status, 301);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem_ab + stage * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
+                    const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
+                    tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
+                    tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp_id == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(256, BN, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs, local++) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                if (!mbar_wait(&bars.tmem_empty[buf], acc_phase ^ 1, bars.abort_flag)) {
+                    atomicExch(status, 302);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&bars.full[stage], phase, bars.abort_flag)) {
+                        atomicExch(status, 303);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_ab + stage * Cfg::kStageBytes);
+                    const uint64_t desc_a = make_desc_sw128(sa);
+                    const uint64_t desc_b = make_desc_sw128(sa + Cfg::kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        umma_i8_pair(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    const uint32_t e = smem_u32(&bars.empty[stage]);
+                    tc_commit_pair(mapa_shared(e, 0));
+                    tc_commit_pair(mapa_shared(e, 1));
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) {
+                    const uint32_t f = smem_u32(&bars.tmem_full[buf]);
+                    tc_commit_pair(mapa_shared(f, 0));
+                    tc_commit_pair(mapa_shared(f, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int q = warp_id & 3;
+        const int epi_tid = (warp_id - 2) * 32 + lane;
+        uint8_t* my_stage = smem_epi + (warp_id - 2) * Cfg::kEpiBufs * Cfg::kEpiBufBytes;
+        constexpr int CH = (EPI == 0) ? 32 : 64;
+        const bool has_bias = (bias != nullptr);
+        int local = 0;
+        int sbuf = 0;
+        bool ok = true;
+        for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+            const TileCoord tc = tile_coord(t, m_blocks, n_blocks, 8);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            const int row0 = tc.a_blk * 256 + (int)rank * 128;
+            const int row = row0 + q * 32 + lane;
+            const int n0 = tc.b_blk * BN;
+            __half* s_ws = smem_scale + buf * 2 * BN;
+            __half* s_bias = s_ws + BN;
+            float as = 0.f;
+            if (EPI == 1) {
+                if (ok) {
+                    for (int i = epi_tid; i < BN; i += kEpiThreads) {
+                        const int n = n0 + i;
+                        s_ws[i] = (n < N) ? w_scale[n] : __float2half(0.f);
+                        s_bias[i] = (has_bias && n < N) ? bias[n] : __float2half(0.f);
+                    }
+                    as = (row < M) ? act_scale[row] : 0.f;
+                }
+                named_barrier_sync(1, kEpiThreads);
+            }
+            if (ok) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag));
+                if (!ok) atomicExch(status, 304);
+            }
+            if (!ok) continue;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / CH; c++) {
+                uint32_t packed[32];
+                if (EPI == 0) {
+                    tmem_ld_32x32b_x32(taddr + c * CH, packed);
+                    tmem_ld_wait();
+                } else {
+                    uint32_t va[32], vb[32];
+                    tmem_ld_32x32b_x32(taddr + c * CH, va);
+                    tmem_ld_32x32b_x32(taddr + c * CH + 32, vb);
+                    tmem_ld_wait();
+                    const __half2* ws2 = reinterpret_cast<const __half2*>(s_ws + c * CH);
+                    const __half2* bs2 = reinterpret_cast<const __half2*>(s_bias + c * CH);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 w = __half22float2(ws2[i]);
+                        const float2 b = __half22float2(bs2[i]);
+                        packed[i] = pack_half2(
+                            dequant_gemm(static_cast<int>(va[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
+                            dequant_gemm(static_cast<int>(va[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 w = __half22float2(ws2[16 + i]);
+                        const float2 b = __half22float2(bs2[16 + i]);
+                        packed[16 + i] = pack_half2(
+                            dequant_gemm(static_cast<int>(vb[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
+                            dequant_gemm(static_cast<int>(vb[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                    }
+                }
+                uint8_t* stg = my_stage + sbuf * Cfg::kEpiBufBytes;
+                if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int chunk = j ^ (lane & 7);
+                    *reinterpret_cast<uint4*>(stg + lane * 128 + chunk * 16) =
+                        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tm_c, stg, n0 + c * CH, row0 + q * 32);
+                    tma_store_commit();
+                }
+                sbuf = (sbuf + 1) % Cfg::kEpiBufs;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*bars.abort_flag != 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA frees TMEM or exits while the peer can still touch it
+    if (warp_id == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ============================================================================================
+// 2:4 sparse: 256 weight rows x BT tokens per pair. CTA r holds compressed weight rows
+// [128r, 128r+128) with their metadata, and token rows [r*BT/2, (r+1)*BT/2) of the tile; its
+// TMEM receives weight rows [128r, 128r+128) x BT token columns.
+
+template <int BT>
+struct SparsePairCfg {
+    static constexpr int HT = BT / 2;                       // tokens staged per CTA
+    static constexpr int kABytes = 128 * 128;
+    static constexpr int kBAtomBytes = HT * 128;
+    static constexpr int kMetaBytes = 128 * 32;
+    static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kFixed = kBarBytes;
+    static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
+    static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
+    static constexpr int kMetaCols = 8 * kStages;
+    static constexpr int kAccBufs = (2 * BT + kMetaCols <= 512) ? 2 : 1;
+    static constexpr int kAccCols = kAccBufs * BT;
+    static constexpr int kTmemCols = 512;
+    static_assert(BT % 32 == 0 && BT <= 256, "pair MMA needs N % 32 == 0, N <= 256");
+    static_assert(kBAtomBytes % 1024 == 0 && kStageBytes % 1024 == 0, "1024-byte aligned operand atoms");
+    static_assert(kStages >= 3, "pipeline depth");
+    static_assert(kAccCols + kMetaCols <= 512, "TMEM capacity");
+};
+
+template <int BT, int EPI>
+__global__ void __launch_bounds__(kSpThreads, 1)
+sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const __grid_constant__ CUtensorMap tm_meta, void* __restrict__ out,
+                   const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
+                   const __half* __restrict__ bias, int M, int N_out, int K, int* __restrict__ status) {
+    using Cfg = SparsePairCfg<BT>;
+    constexpr int HT = Cfg::HT;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* smem_stage = smem;
+    const PairBars bars = carve_bars(smem + Cfg::kStages * Cfg::kStageBytes, Cfg::kStages);
+
+    const int warp_id = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = (rank == 0);
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(status, 400);
+        return;
+    }
+
+    const int w_blocks = (N_out + 255) / 256;
+    const int t_blocks = (M + BT - 1) / BT;
+    const int num_tiles = w_blocks * t_blocks;
+    const int num_kb = (K + 255) / 256;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) init_bars(bars, Cfg::kStages, kSpEpiWarps);
+    if (warp_id == 0 && lane == 0) {
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_x);
+        prefetch_tensormap(&tm_meta);
+    }
+    if (warp_id == 1) {
+        tmem_alloc_pair(bars.tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *bars.tmem_slot;
+    const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
+
+    if (warp_id == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const int w_row = tc.a_blk * 256 + (int)rank * 128;
+                const int t_row = tc.b_blk * BT + (int)rank * HT;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
+                        atomicExch(status, 401);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
+                    if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
+                    const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
+                    tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
+                    tma_load_2d_pair(sb, &tm_x, full_leader, kb * 256, t_row);
+                    tma_load_2d_pair(sb + Cfg::kBAtomBytes, &tm_x, full_leader, kb * 256 + 128, t_row);
+                    tma_load_3d_pair(sm, &tm_meta, full_leader, 0, w_row, kb * 2);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp_id == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(256, BT, true);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs, local++) {
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                if (!mbar_wait(&bars.tmem_empty[buf], acc_phase ^ 1, bars.abort_flag)) {
+                    atomicExch(status, 402);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * BT;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&bars.full[stage], phase, bars.abort_flag)) {
+                        atomicExch(status, 403);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_stage + stage * Cfg::kStageBytes);
+                    const uint32_t sb = sa + Cfg::kABytes;
+                    const uint32_t sm = sb + 2 * Cfg::kBAtomBytes;
+                    const uint32_t te = tmem_meta + 8 * stage;
+                    tmem_cp_128x128b_pair(te, make_desc_noswizzle(sm, 2048, 128));
+                    tmem_cp_128x128b_pair(te + 4, make_desc_noswizzle(sm + 2048, 2048, 128));
+                    const uint64_t desc_a = make_desc_sw128(sa);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint64_t desc_b = make_desc_sw128(sb + (j >> 1) * Cfg::kBAtomBytes) + 4 * (j & 1);
+                        umma_i8_sp_pair(tmem_acc, desc_a + 2 * j, desc_b, te + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    const uint32_t e = smem_u32(&bars.empty[stage]);
+                    tc_commit_pair(mapa_shared(e, 0));
+                    tc_commit_pair(mapa_shared(e, 1));
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) {
+                    const uint32_t f = smem_u32(&bars.tmem_full[buf]);
+                    tc_commit_pair(mapa_shared(f, 0));
+                    tc_commit_pair(mapa_shared(f, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int q = warp_id & 3;
+        const int chunk0 = (warp_id - 2) >> 2;
+        const bool has_bias = (bias != nullptr);
+        int local = 0;
+        for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+            const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+            const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+            const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+            const int n = tc.a_blk * 256 + (int)rank * 128 + q * 32 + lane;
+            const int m0 = tc.b_blk * BT;
+            float ws = 0.f, bs = 0.f;
+            if (EPI == 1 && n < N_out) {
+                ws = __half2float(w_scale[n]);
+                if (has_bias) bs = __half2float(bias[n]);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag))) {
+                atomicExch(status, 404);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+            for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
+                const int m_first = m0 + c * 32;
+                if (m_first >= M) break;
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, v);
+                float as_lane = 0.f;
+                if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
+                tmem_ld_wait();
+                store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*bars.abort_flag != 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp_id == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ============================================================================================
+// Host side.
+
+// Launches `kern` as clusters of two CTAs; grid = 2 x min(tiles, co-resident clusters).
+// Returns kOk, kLaunchFailed, or -1 when no cluster of this kernel fits (caller falls back to the
+// single-CTA kernel).
+template <typename Kern, typename... Args>
+int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaStream_t stream,
+                 int* max_pairs_cache, Args... args) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int& max_pairs = max_pairs_cache[dev & 63];
+    if (max_pairs == 0) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
+            return kLaunchFailed;
+        cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            max_pairs = -1;
+        } else {
+            max_pairs = n;
+        }
+    }
+    if (max_pairs < 0) return -1;
+    const int pairs = (int)std::min<long long>(tiles, max_pairs);
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+    return e == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+template <int EPI>
+int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
+                      const __half* bias, void* out, int M, int K, int N, cudaStream_t stream) {
+    static int max_pairs[64] = {};
+    CUtensorMap tm_a, tm_b, tm_c;
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {128, 128};
+        if (!make_tmap(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {128, 128};
+        if (!make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t esz = (EPI == 0) ? 4 : 2;
+        const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)N * esz};
+        const uint32_t box[2] = {(uint32_t)(128 / esz), 32};
+        const CUtensorMapDataType dt = (EPI == 0) ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if (!make_tmap(&tm_c, dt, 2, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return kLaunchFailed;
+    }
+    int* status = status_word();
+    if (status == nullptr) return kLaunchFailed;
+    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    return launch_pairs(dense_pair_kernel<EPI>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b, tm_c,
+                        act_scale, w_scale, bias, M, N, K, status);
+}
+
+template <int BT, int EPI>
+int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                       const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
+                       cudaStream_t stream) {
+    using Cfg = SparsePairCfg<BT>;
+    static int max_pairs[64] = {};
+    CUtensorMap tm_w, tm_x, tm_meta;
+    {
+        const uint64_t dims[2] = {(uint64_t)K / 2, (uint64_t)N_out};
+        const uint64_t str[1] = {(uint64_t)K / 2};
+        const uint32_t box[2] = {128, 128};
+        if (!make_tmap(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W_comp, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {128, (uint32_t)Cfg::HT};
+        if (!make_tmap(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
+        const uint64_t dims[3] = {4, (uint64_t)N_out, (uint64_t)K / 128};
+        const uint64_t str[2] = {(uint64_t)K / 8, 16};
+        const uint32_t box[3] = {4, 128, 2};
+        if (!make_tmap(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w_meta, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return kLaunchFailed;
+    }
+    int* status = status_word();
+    if (status == nullptr) return kLaunchFailed;
+    const long long tiles = (long long)((N_out + 255) / 256) * ((M + BT - 1) / BT);
+    return launch_pairs(sparse_pair_kernel<BT, EPI>, kSpThreads, Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x, tm_meta,
+                        out, act_scale, w_scale, bias, M, N_out, K, status);
+}
+
+template <int EPI>
+int sparse_pair_dispatch(int bt, const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
+                         const float* act_scale, const __half* w_scale, const __half* bias, void* out, int M, int K,
+                         int N_out, cudaStream_t stream) {
+    switch (bt) {
+    case 128: return launch_sparse_pair<128, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    case 192: return launch_sparse_pair<192, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    case 256: return launch_sparse_pair<256, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    default:  return launch_sparse_pair<224, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    }
+}
+
+}  // namespace
+
+int dense_pair_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K, int N, cudaStream_t stream) {
+    return launch_dense_pair<0>(A, B, nullptr, nullptr, nullptr, out, M, K, N, stream);
+}
+
+int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
+                       const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream) {
+    return launch_dense_pair<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+}
+
+int sparse_pair_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,
+                    int N_out, cudaStream_t stream, int bt) {
+    return sparse_pair_dispatch<0>(bt, W_comp, x, w_meta, nullptr, nullptr, nullptr, out, M, K, N_out, stream);
+}
+
+int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                        const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
+                        cudaStream_t stream, int bt) {
+    return sparse_pair_dispatch<1>(bt, W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+}
+
+}  // namespace fb200

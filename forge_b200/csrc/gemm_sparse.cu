@@ -17,12 +17,15 @@
 //              (row-major uint32, nibble g at bits [4g,4g+4)) is already what the tensor core
 //              expects per lane: 2 columns per 64-deep step - then four
 //              tcgen05.mma.sp kind::i8 (M=128, N=BT, K=64) per slab.
-//   warps 2-5: epilogue. tcgen05.ld (lane = weight row, registers = tokens), dequantise,
-//              transpose through shared memory ([token][weight row]) and TMA-store.
+//   warps 2-5: epilogue. tcgen05.ld (lane = weight row, registers = tokens), dequantise, and
+//              store straight to global memory: for one token the 32 lanes of a warp hold 32
+//              consecutive output columns, so every warp store is one contiguous segment.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "gemm_dense.cuh"
 #include "gemm_sparse.cuh"
+#include "gemm_pair.cuh"
+#include "sparse_epilogue.cuh"
 
 namespace fb200 {
 
@@ -32,10 +35,9 @@ namespace {
 
 constexpr int BW = 128;          // weight rows per tile (UMMA M)
 constexpr int SLAB_K = 256;      // logical K per pipeline stage
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;             // two warps per TMEM lane quarter, alternating 32-token chunks
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kMetaBytes = BW * 32;        // 128 rows x 32 bytes per slab
-constexpr int kStageOutBytes = 16 * 1024;  // epilogue staging, used as two 8 KB halves
 
 template <int BT>
 struct SparseCfg {
@@ -43,9 +45,8 @@ struct SparseCfg {
     static constexpr int kBAtomBytes = BT * 128;
     static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
     static constexpr int kAccBufs = (2 * BT + 32 <= 512) ? 2 : 1;
-    static constexpr int kScaleBytes = 2 * BT * (int)sizeof(float);
     static constexpr int kBarBytes = 256;
-    static constexpr int kFixed = kStageOutBytes + kScaleBytes + kBarBytes;
+    static constexpr int kFixed = kBarBytes;
     static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesMax > 8 ? 8 : kStagesMax;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
@@ -81,16 +82,14 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int w_blocks, int t_block
 template <int BT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_out,
+                   const __grid_constant__ CUtensorMap tm_meta, void* __restrict__ out,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, int M, int N_out, int K, int* __restrict__ status) {
     using Cfg = SparseCfg<BT>;
     extern __shared__ __align__(1024) uint8_t smem[];
 
     uint8_t* smem_stage = smem;
-    uint8_t* smem_out = smem + Cfg::kStages * Cfg::kStageBytes;
-    float* smem_as = reinterpret_cast<float*>(smem_out + kStageOutBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_out + kStageOutBytes + Cfg::kScaleBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + Cfg::kStages;
     uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -118,7 +117,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4);
+            mbar_init(&tmem_empty[b], kEpiWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -127,7 +126,6 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         prefetch_tensormap(&tm_w);
         prefetch_tensormap(&tm_x);
         prefetch_tensormap(&tm_meta);
-        prefetch_tensormap(&tm_out);
     }
     if (warp_id == 1) {
         tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
@@ -197,7 +195,9 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     const uint32_t sb = sa + Cfg::kABytes;
                     const uint32_t sm = sb + 2 * Cfg::kBAtomBytes;
                     const uint32_t te = tmem_meta + 8 * stage;
-                    // metadata: two 16-byte columns of 128 rows -> 2 x 4 TMEM columns
+                    // metadata: two 16-byte columns of 128 rows -> 2 x 4 TMEM columns. (Copying it one
+                    // slab ahead of its MMAs was measured and is slower: the wait for the next stage
+                    // then delays MMAs whose operands are already resident.)
                     tmem_cp_128x128b(te, make_desc_noswizzle(sm, 2048, 128));
                     tmem_cp_128x128b(te + 4, make_desc_noswizzle(sm + 2048, 2048, 128));
                     const uint64_t desc_a = make_desc_sw128(sa);
@@ -218,82 +218,43 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
     } else {
         // ------------------------------------------------------------------ epilogue
-        const int q = warp_id & 3;
-        const int epi_tid = (warp_id - 2) * 32 + lane;
-        constexpr int TOK = (EPI == 0) ? 16 : 32;              // tokens per staged chunk (8 KB)
-        constexpr int ROW_BYTES = BW * ((EPI == 0) ? 4 : 2);   // one token's 128 outputs
+        const int q = warp_id & 3;                 // TMEM lane quarter this warp may read
+        const int chunk0 = (warp_id - 2) >> 2;     // 0 or 1: which alternate chunks this warp takes
         const bool has_bias = (bias != nullptr);
         int local = 0;
-        int half = 0;
-        bool ok = true;   // after a failed wait: keep meeting the named barriers, touch nothing
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
             const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
             const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
             const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
             const int n = tc.w_blk * BW + q * 32 + lane;   // this thread's weight row = output column
             const int m0 = tc.t_blk * BT;
-            float* s_as = smem_as + (local & 1) * BT;
             float ws = 0.f, bs = 0.f;
-            if (EPI == 1) {
-                if (ok) {
-                    for (int i = epi_tid; i < BT; i += kEpiThreads) s_as[i] = (m0 + i < M) ? act_scale[m0 + i] : 0.f;
-                    if (n < N_out) {
-                        ws = __half2float(w_scale[n]);
-                        if (has_bias) bs = __half2float(bias[n]);
-                    }
-                }
-                named_barrier_sync(1, kEpiThreads);
+            if (EPI == 1 && n < N_out) {
+                ws = __half2float(w_scale[n]);
+                if (has_bias) bs = __half2float(bias[n]);
             }
-            if (ok) {
-                // warp-uniform outcome: the TMEM loads below are .sync.aligned
-                ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag));
-                if (!ok) atomicExch(status, 204);
+            // warp-uniform outcome: the TMEM loads below are .sync.aligned
+            if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag))) {
+                atomicExch(status, 204);
+                break;
             }
-            if (ok) tc_fence_after();
+            tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
 #pragma unroll 1
-            for (int c = 0; c < BT / 32; c++) {
+            for (int c = chunk0; c < BT / 32; c += kEpiWarps / 4) {
+                const int m_first = m0 + c * 32;
+                if (m_first >= M) break;   // warp-uniform: the rest of the tile is past the last token
                 uint32_t v[32];
-                if (ok) {
-                    tmem_ld_32x32b_x32(taddr + c * 32, v);
-                    tmem_ld_wait();
-                }
-#pragma unroll
-                for (int h = 0; h < 32 / TOK; h++) {
-                    uint8_t* stg = smem_out + half * (kStageOutBytes / 2);
-                    // the TMA store that last read this half must be done with it
-                    if (epi_tid == 0) tma_store_wait_read<1>();
-                    named_barrier_sync(2, kEpiThreads);
-                    if (ok) {
-#pragma unroll
-                        for (int j = 0; j < TOK; j++) {
-                            const int tok = c * 32 + h * TOK + j;
-                            const int acc = static_cast<int>(v[h * TOK + j]);
-                            if (EPI == 0) {
-                                *reinterpret_cast<int32_t*>(stg + j * ROW_BYTES + (q * 32 + lane) * 4) = acc;
-                            } else {
-                                const float o = dequant_gemm(acc, mul_ftz(s_as[tok], ws), bs, has_bias);
-                                *reinterpret_cast<__half*>(stg + j * ROW_BYTES + (q * 32 + lane) * 2) =
-                                    __float2half_rn(o);
-                            }
-                        }
-                        fence_proxy_async_smem();
-                    }
-                    named_barrier_sync(3, kEpiThreads);
-                    if (ok && epi_tid == 0) {
-                        tma_store_2d(&tm_out, stg, tc.w_blk * BW, m0 + c * 32 + h * TOK);
-                        tma_store_commit();
-                    }
-                    half ^= 1;
-                }
+                tmem_ld_32x32b_x32(taddr + c * 32, v);
+                float as_lane = 0.f;
+                if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
+                tmem_ld_wait();
+                store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
             }
-            if (ok) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
-        if (epi_tid == 0) tma_store_wait_all<0>();
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -350,7 +311,7 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
             return kLaunchFailed;
         attr_set[dev & 63] = true;
     }
-    CUtensorMap tm_w, tm_x, tm_meta, tm_out;
+    CUtensorMap tm_w, tm_x, tm_meta;
     {
         const uint64_t dims[2] = {(uint64_t)K / 2, (uint64_t)N_out};
         const uint64_t str[1] = {(uint64_t)K / 2};
@@ -374,19 +335,11 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
                        CU_TENSOR_MAP_SWIZZLE_NONE))
             return kLaunchFailed;
     }
-    {
-        const uint64_t esz = (EPI == 0) ? 4 : 2;
-        const uint64_t dims[2] = {(uint64_t)N_out, (uint64_t)M};
-        const uint64_t str[1] = {(uint64_t)N_out * esz};
-        const uint32_t box[2] = {BW, (uint32_t)((EPI == 0) ? 16 : 32)};
-        const CUtensorMapDataType dt = (EPI == 0) ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-        if (!make_tmap(&tm_out, dt, 2, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return kLaunchFailed;
-    }
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((N_out + BW - 1) / BW) * ((M + BT - 1) / BT);
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_out, act_scale, w_scale, bias, M,
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, out, act_scale, w_scale, bias, M,
                                                       N_out, K, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
@@ -399,14 +352,30 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
     if (W_comp == nullptr || x == nullptr || w_meta == nullptr || out == nullptr) return kBadPointer;
     if (EPI == 1 && (act_scale == nullptr || w_scale == nullptr)) return kBadPointer;
     if (!device_is_sm100()) return kUnsupportedArch;
-    const int out_esz = (EPI == 0) ? 4 : 2;
-    const bool tma_ok = (K % 128 == 0) && ((long long)N_out * out_esz % 16 == 0) && aligned16(W_comp) &&
-                        aligned16(x) && aligned16(w_meta) && aligned16(out);
+    const bool tma_ok = (K % 128 == 0) && aligned16(W_comp) && aligned16(x) && aligned16(w_meta);
     if (!tma_ok) {
         const long long total = (long long)M * N_out;
         sparse_gemm_ragged_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
             W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+    // 1000 + BT: the CTA-pair kernel (256 weight rows x BT tokens per pair of SMs).
+    if (force_bt > 1000) {
+        const int r = (EPI == 0) ? sparse_pair_s32(W_comp, x, w_meta, static_cast<int32_t*>(out), M, K, N_out,
+                                                   stream, force_bt - 1000)
+                                 : sparse_pair_dequant(W_comp, x, w_meta, act_scale, w_scale, bias,
+                                                       static_cast<__half*>(out), M, K, N_out, stream,
+                                                       force_bt - 1000);
+        if (r >= 0) return r;
+    }
+    // Large problems: 256 weight rows x 224 tokens per CTA pair (measured fastest from M = N_out = 8192,
+    // K >= 1024 down to the 11008 x 4096 weight of a Llama MLP).
+    if (force_bt == 0 && M >= 1024 && N_out >= 512) {
+        const int r = (EPI == 0) ? sparse_pair_s32(W_comp, x, w_meta, static_cast<int32_t*>(out), M, K, N_out,
+                                                   stream, 224)
+                                 : sparse_pair_dequant(W_comp, x, w_meta, act_scale, w_scale, bias,
+                                                       static_cast<__half*>(out), M, K, N_out, stream, 224);
+        if (r >= 0) return r;
     }
     int bt = force_bt;
     if (bt != 32 && bt != 64 && bt != 128) {

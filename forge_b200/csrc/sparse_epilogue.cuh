@@ -1,0 +1,56 @@
+// Epilogue of the 2:4-sparse GEMM kernels. The sparse operand is the MMA's A operand, so the
+// accumulator is the transpose of the output: TMEM lane = weight row n (an output COLUMN),
+// TMEM column = token m (an output ROW). After tcgen05.ld a thread holds 32 consecutive tokens
+// of one output column, and the 32 lanes of a warp hold 32 consecutive columns - so a plain
+// store per token writes 32 consecutive elements (64 or 128 contiguous bytes) per warp
+// instruction: coalesced without any staging in shared memory.
+#pragma once
+
+#include "common.cuh"
+
+namespace fb200 {
+
+// v[j]: accumulator of token (m_first + j) for output column n. EPI 0: raw s32, 1: fp16 dequant.
+// as_lane: act_scale[m_first + lane] (0 past the end), broadcast per token with a shuffle.
+template <int EPI>
+__device__ __forceinline__ void store_transposed_chunk(const uint32_t (&v)[32], void* __restrict__ out, int N_out,
+                                                       int M, int n, int m_first, float as_lane, float ws, float bs,
+                                                       bool has_bias) {
+    const int valid = min(32, M - m_first);   // warp-uniform
+    const bool col_ok = n < N_out;
+    // interior chunks (the common case) take the unguarded path: no per-element branches
+    const bool full = (valid == 32) && __all_sync(0xffffffffu, col_ok);
+    if (EPI == 0) {
+        int32_t* p = static_cast<int32_t*>(out) + (size_t)m_first * N_out + n;
+        if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) p[(size_t)j * N_out] = static_cast<int32_t>(v[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                if (j < valid && col_ok) p[(size_t)j * N_out] = static_cast<int32_t>(v[j]);
+            }
+        }
+    } else {
+        __half* p = static_cast<__half*>(out) + (size_t)m_first * N_out + n;
+        if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float as = __shfl_sync(0xffffffffu, as_lane, j);
+                const float o = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
+                p[(size_t)j * N_out] = __float2half_rn(o);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float as = __shfl_sync(0xffffffffu, as_lane, j);
+                if (j < valid && col_ok) {
+                    const float o = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
+                    p[(size_t)j * N_out] = __float2half_rn(o);
+                }
+            }
+        }
+    }
+}
+
+}  // namespace fb200

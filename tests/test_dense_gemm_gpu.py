@@ -85,6 +85,25 @@ def test_every_tile_width(bn):
     assert np.array_equal(out16.cpu().numpy().view(np.uint16), want.view(np.uint16))
 
 
+@pytest.mark.parametrize("M,K,N", [(256, 128, 256), (300, 640, 272), (1024, 1024, 1024), (2050, 512, 400),
+                                   (257, 144, 520), (512, 4096, 768)])
+def test_cta_pair_kernel(M, K, N):
+    """The cta_group::2 kernel (256 x 256 outputs per pair of SMs), selected with tile knob 512."""
+    A, B, a_s, w_s, bias = _inputs(M, K, N, 77 + M + K + N)
+    lib = _lib.load()
+    lib.forge_b200_set_dense_tile(512)
+    try:
+        out = C.int8_gemm_s32(A.to(DEV), B.to(DEV))
+        out16 = C.int8_gemm_dequant(A.to(DEV), B.to(DEV), a_s.to(DEV), w_s.to(DEV), bias.to(DEV))
+        _status_ok()
+    finally:
+        lib.forge_b200_set_dense_tile(0)
+    acc = O.gemm_s32(A.numpy(), B.numpy())
+    assert np.array_equal(out.cpu().numpy(), acc)
+    want = O.dequantize_bias(acc, a_s.numpy(), w_s.numpy(), bias.numpy(), gemm_epilogue=True)
+    assert np.array_equal(out16.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
 def test_headline_8192_sampled_rows_and_determinism():
     M = K = N = 8192
     g = torch.Generator(device=DEV).manual_seed(1234)

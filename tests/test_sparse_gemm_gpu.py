@@ -79,6 +79,26 @@ def test_dequant_bit_exact_every_tile(M, K, N, tile):
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "differs from the reference mma.sp kernel"
 
 
+@pytest.mark.parametrize("bt", [128, 192, 224, 256])
+@pytest.mark.parametrize("M,K,N", [(37, 256, 208), (300, 1280, 384), (1000, 1536, 512), (2050, 512, 400)])
+def test_cta_pair_kernel_every_token_tile(bt, M, K, N):
+    """The cta_group::2 kernel (256 weight rows x bt tokens per pair of SMs), knob 1000 + bt."""
+    W, x, a_s, w_s, bias, comp, packed = _prep(M, K, N, 3 + bt + M + K + N)
+    lib = _lib.load()
+    dx = x.to(DEV)
+    lib.forge_b200_set_sparse_tile(1000 + bt)
+    try:
+        out = C.sparse_int8_gemm_s32(comp, dx, packed)
+        out16 = C.sparse_int8_gemm(comp, dx, packed, a_s.to(DEV), w_s.to(DEV), bias.to(DEV))
+        _status_ok()
+    finally:
+        lib.forge_b200_set_sparse_tile(0)
+    acc = O.gemm_s32(x.numpy(), O.prune_24_dense(W.numpy()))
+    assert np.array_equal(out.cpu().numpy(), acc)
+    want = O.dequantize_bias(acc, a_s.numpy(), w_s.numpy(), bias.numpy(), gemm_epilogue=True)
+    assert np.array_equal(out16.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
 def test_every_nibble_in_every_group_position():
     """128 weight rows x K=64: each of the six valid 2:4 codes placed at each of the 16 group
     positions of a 64-deep step, against the dense host loop."""
@@ -103,7 +123,7 @@ def test_every_nibble_in_every_group_position():
     assert np.array_equal(out.cpu().numpy(), O.gemm_s32(x.numpy(), W))
 
 
-@pytest.mark.parametrize("M", [1, 16, 128, 2048])
+@pytest.mark.parametrize("M", [1, 16, 128, 2048, 8192])
 def test_config3_shape_sampled(M):
     """BASELINE config 3 (N=11008, K=4096): sparse result equals the dense GEMM on the pruned
     weights, exact, on sampled tokens; repeat runs identical."""
