@@ -32,6 +32,11 @@ SIGNATURES = {
     "forge_sparse_int8_linear": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i],
     "forge_splitk_reduce": [_vp, _vp, _vp, _i, _i, _vp],
     "forge_sparse_int8_gemm_s32": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "forge_int8_gated_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "forge_sparse_int8_gated_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "forge_w8a8_gated_mlp_workspace_bytes": [_i, _i, _i],
+    "forge_w8a8_gated_mlp": [_vp] * 11 + [_i, _i, _i, _vp, _vp],
+    "forge_sparse_w8a8_gated_mlp": [_vp] * 14 + [_i, _i, _i, _vp, _vp],
     "forge_prune_compress_24": [_vp, _vp, _vp, _i, _i, _vp],
     "forge_pack_metadata": [_vp, _vp, _i, _i, _vp],
     "forge_b200_set_dense_tile": [_i],
@@ -65,6 +70,8 @@ def load():
             fn.restype = None
         elif name == "forge_b200_status_string":
             fn.restype = ctypes.c_char_p
+        elif name == "forge_w8a8_gated_mlp_workspace_bytes":
+            fn.restype = ctypes.c_ulonglong
         else:
             fn.restype = ctypes.c_int
     _lib = lib

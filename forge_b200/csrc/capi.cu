@@ -165,6 +165,95 @@ int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const
     return sparse_gemm_s32(W_comp, x_int8, w_meta, output, M, K, N_out, S(stream), g_force_sparse_bt);
 }
 
+int forge_int8_gated_gemm(const int8_t* x_int8, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                          const void* wg_scale, const void* wu_scale, const void* bg, const void* bu, void* h_out,
+                          int M, int K, int N, forge_stream_t stream) {
+    return dense_gemm_gated(x_int8, Wg, Wu, act_scale, H(wg_scale), H(wu_scale), H(bg), H(bu), H(h_out), M, K, N,
+                            S(stream));
+}
+
+int forge_sparse_int8_gated_gemm(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp,
+                                 const uint32_t* wu_meta, const int8_t* x_int8, const float* act_scale,
+                                 const void* wg_scale, const void* wu_scale, const void* bg, const void* bu,
+                                 void* h_out, int M, int K, int N_out, forge_stream_t stream) {
+    return sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, x_int8, act_scale, H(wg_scale), H(wu_scale), H(bg),
+                             H(bu), H(h_out), M, K, N_out, S(stream), g_force_sparse_bt);
+}
+
+namespace {
+
+inline size_t pad256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
+
+struct MlpWorkspace {
+    int8_t* xq;
+    float* xs;
+    __half* h;
+    int8_t* hq;
+    float* hs;
+    size_t bytes;
+};
+
+inline MlpWorkspace carve_mlp_workspace(void* base, int M, int d_model, int d_ffn) {
+    MlpWorkspace w;
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    w.xq = reinterpret_cast<int8_t*>(p + off);
+    off += pad256((size_t)M * d_model);
+    w.xs = reinterpret_cast<float*>(p + off);
+    off += pad256((size_t)M * sizeof(float));
+    w.h = reinterpret_cast<__half*>(p + off);
+    off += pad256((size_t)M * d_ffn * sizeof(__half));
+    w.hq = reinterpret_cast<int8_t*>(p + off);
+    off += pad256((size_t)M * d_ffn);
+    w.hs = reinterpret_cast<float*>(p + off);
+    off += pad256((size_t)M * sizeof(float));
+    w.bytes = off;
+    return w;
+}
+
+}  // namespace
+
+unsigned long long forge_w8a8_gated_mlp_workspace_bytes(int M, int d_model, int d_ffn) {
+    if (M <= 0 || d_model <= 0 || d_ffn <= 0) return 0;
+    return carve_mlp_workspace(nullptr, M, d_model, d_ffn).bytes;
+}
+
+int forge_w8a8_gated_mlp(const void* x, const int8_t* Wg, const int8_t* Wu, const int8_t* Wd, const void* wg_scale,
+                         const void* wu_scale, const void* wd_scale, const void* bg, const void* bu, const void* bd,
+                         void* out, int M, int d_model, int d_ffn, void* workspace, forge_stream_t stream) {
+    if (M <= 0 || d_model <= 0 || d_ffn <= 0) return kOk;
+    if (x == nullptr || workspace == nullptr || out == nullptr) return kBadPointer;
+    const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
+    int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
+    if (r != kOk) return r;
+    r = dense_gemm_gated(w.xq, Wg, Wu, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h, M, d_model, d_ffn,
+                         S(stream));
+    if (r != kOk) return r;
+    r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
+    if (r != kOk) return r;
+    return dense_gemm_dequant(w.hq, Wd, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
+                              g_force_dense_bn);
+}
+
+int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp,
+                                const uint32_t* wu_meta, const int8_t* Wd_comp, const uint32_t* wd_meta,
+                                const void* wg_scale, const void* wu_scale, const void* wd_scale, const void* bg,
+                                const void* bu, const void* bd, void* out, int M, int d_model, int d_ffn,
+                                void* workspace, forge_stream_t stream) {
+    if (M <= 0 || d_model <= 0 || d_ffn <= 0) return kOk;
+    if (x == nullptr || workspace == nullptr || out == nullptr) return kBadPointer;
+    const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
+    int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
+    if (r != kOk) return r;
+    r = sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, w.xq, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h,
+                          M, d_model, d_ffn, S(stream), g_force_sparse_bt);
+    if (r != kOk) return r;
+    r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
+    if (r != kOk) return r;
+    return sparse_gemm_dequant(Wd_comp, w.hq, wd_meta, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
+                               g_force_sparse_bt);
+}
+
 int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
                             forge_stream_t stream) {
     return prune_compress_24(weight, compressed, metadata_raw, N, K, S(stream));

@@ -118,6 +118,13 @@ __device__ __forceinline__ float dequant_gemm(int acc, float as_ws, float bias, 
     return has_bias ? fma_ftz(a, as_ws, bias) : mul_ftz(a, as_ws);
 }
 
+// SiLU(g) * u in fp32: g / (1 + exp(-g)) * u, with the fast exponential and division (the
+// composition is this library's own; the reference has no gated epilogue). One fp16 rounding
+// happens at the caller.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
     return *reinterpret_cast<const uint32_t*>(&h);

@@ -66,13 +66,17 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
     return c;
 }
 
-// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias).
+// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias),
+//      2 = gated: the B tile is 128 rows of a gate weight followed by the same 128 rows of an up
+//          weight (tm_b / tm_b2), so accumulator columns c and 128 + c belong to output column c of
+//          the same token; the epilogue writes fp16(SiLU(g) * u) with g, u dequantised in fp32.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ act_scale,
-                  const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
-                  int* __restrict__ status) {
+                  const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
+                  const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
+                  const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
+                  const __half* __restrict__ bias2, int M, int N, int K, int* __restrict__ status) {
     using Cfg = DenseCfg<BN>;
     extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -96,7 +100,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
 
     const int m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
-    const int n_blocks = (N + BN - 1) / BN;
+    constexpr int TILE_N = (EPI == 2) ? BN / 2 : BN;   // output columns per tile
+    const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const int num_tiles = m_blocks * n_blocks;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
 
@@ -115,6 +120,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (warp_id == 0 && lane == 0) {
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
+        if (EPI == 2) prefetch_tensormap(&tm_b2);
         prefetch_tensormap(&tm_c);
     }
     if (warp_id == 1) {
@@ -144,7 +150,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     uint8_t* sb = sa + Cfg::kABytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
                     tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, tc.m_blk * BLOCK_M);
-                    tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * BN);
+                    if (EPI == 2) {
+                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
+                        tma_load_2d(sb + Cfg::kBBytes / 2, &tm_b2, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
+                    } else {
+                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * BN);
+                    }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -211,16 +222,23 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row = tc.m_blk * BLOCK_M + q * 32 + lane;
-            const int n0 = tc.n_blk * BN;
+            const int n0 = tc.n_blk * TILE_N;
+            // EPI 1: [w_scale BN][bias BN]; EPI 2: [gate scale][gate bias][up scale][up bias], TILE_N each
             __half* s_ws = smem_scale + buf * 2 * BN;
-            __half* s_bias = s_ws + BN;
+            __half* s_bias = s_ws + TILE_N;
+            __half* s_ws2 = s_bias + TILE_N;
+            __half* s_bias2 = s_ws2 + TILE_N;
             float as = 0.f;
-            if (EPI == 1) {
+            if (EPI != 0) {
                 if (ok) {
-                    for (int i = epi_tid; i < BN; i += kEpiWarps * 32) {
+                    for (int i = epi_tid; i < TILE_N; i += kEpiWarps * 32) {
                         const int n = n0 + i;
                         s_ws[i] = (n < N) ? w_scale[n] : __float2half(0.f);
                         s_bias[i] = (has_bias && n < N) ? bias[n] : __float2half(0.f);
+                        if (EPI == 2) {
+                            s_ws2[i] = (n < N) ? w_scale2[n] : __float2half(0.f);
+                            s_bias2[i] = (bias2 != nullptr && n < N) ? bias2[n] : __float2half(0.f);
+                        }
                     }
                     as = (row < M) ? act_scale[row] : 0.f;
                 }
@@ -235,12 +253,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / CH; c++) {
+            for (int c = 0; c < TILE_N / CH; c++) {
                 uint32_t packed[32];
                 if (EPI == 0) {
                     tmem_ld_32x32b_x32(taddr + c * CH, packed);
                     tmem_ld_wait();
-                } else {
+                } else if (EPI == 1) {
                     uint32_t va[32], vb[32];
                     tmem_ld_32x32b_x32(taddr + c * CH, va);
                     tmem_ld_32x32b_x32(taddr + c * CH + 32, vb);
@@ -262,6 +280,32 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         packed[16 + i] = pack_half2(
                             dequant_gemm(static_cast<int>(vb[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
                             dequant_gemm(static_cast<int>(vb[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                    }
+                } else {
+                    const bool has_bias2 = (bias2 != nullptr);
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {   // two 32-column halves of the 64-column staged row
+                        uint32_t vg[32], vu[32];
+                        const int col = c * CH + hh * 32;
+                        tmem_ld_32x32b_x32(taddr + col, vg);
+                        tmem_ld_32x32b_x32(taddr + TILE_N + col, vu);
+                        tmem_ld_wait();
+                        const __half2* gs2 = reinterpret_cast<const __half2*>(s_ws + col);
+                        const __half2* gb2 = reinterpret_cast<const __half2*>(s_bias + col);
+                        const __half2* us2 = reinterpret_cast<const __half2*>(s_ws2 + col);
+                        const __half2* ub2 = reinterpret_cast<const __half2*>(s_bias2 + col);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const float2 gw = __half22float2(gs2[i]), gb = __half22float2(gb2[i]);
+                            const float2 uw = __half22float2(us2[i]), ub = __half22float2(ub2[i]);
+                            const float g0 = dequant_gemm(static_cast<int>(vg[2 * i]), mul_ftz(as, gw.x), gb.x, has_bias);
+                            const float g1 =
+                                dequant_gemm(static_cast<int>(vg[2 * i + 1]), mul_ftz(as, gw.y), gb.y, has_bias);
+                            const float u0 = dequant_gemm(static_cast<int>(vu[2 * i]), mul_ftz(as, uw.x), ub.x, has_bias2);
+                            const float u1 =
+                                dequant_gemm(static_cast<int>(vu[2 * i + 1]), mul_ftz(as, uw.y), ub.y, has_bias2);
+                            packed[hh * 16 + i] = pack_half2(silu_mul(g0, u0), silu_mul(g1, u1));
+                        }
                     }
                 }
                 uint8_t* stg = my_stage + sbuf * kEpiBufBytes;
@@ -329,7 +373,8 @@ __global__ void dense_gemm_ragged_kernel(const int8_t* __restrict__ A, const int
 
 template <int BN, int EPI>
 int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale, const __half* bias,
-                 void* out, int M, int K, int N, cudaStream_t stream) {
+                 void* out, int M, int K, int N, cudaStream_t stream, const int8_t* B2 = nullptr,
+                 const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
     using Cfg = DenseCfg<BN>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -340,7 +385,8 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
             return kLaunchFailed;
         attr_set[dev & 63] = true;
     }
-    CUtensorMap tm_a, tm_b, tm_c;
+    constexpr int TILE_N = (EPI == 2) ? BN / 2 : BN;
+    CUtensorMap tm_a, tm_b, tm_b2, tm_c;
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         const uint64_t str[1] = {(uint64_t)K};
@@ -351,8 +397,11 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
         const uint64_t str[1] = {(uint64_t)K};
-        const uint32_t box[2] = {BLOCK_K, BN};
+        const uint32_t box[2] = {BLOCK_K, TILE_N};
         if (!make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+        if (!make_tmap(&tm_b2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (EPI == 2) ? B2 : B, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
     }
     {
@@ -366,10 +415,11 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     const int m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
-    const int n_blocks = (N + BN - 1) / BN;
+    const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const long long tiles = (long long)m_blocks * n_blocks;
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, tm_c, act_scale, w_scale, bias, M, N, K, status);
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, tm_b2, tm_c, act_scale, w_scale, bias, w_scale2,
+                                                      bias2, M, N, K, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -424,6 +474,20 @@ int dense_gemm_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K,
 int dense_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream, int force_bn) {
     return dense_dispatch<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream, force_bn);
+}
+
+int dense_gemm_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                     const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,
+                     int M, int K, int N, cudaStream_t stream) {
+    if (M <= 0 || K <= 0 || N <= 0) return kOk;
+    if (A == nullptr || Wg == nullptr || Wu == nullptr || act_scale == nullptr || wg_scale == nullptr ||
+        wu_scale == nullptr || out == nullptr)
+        return kBadPointer;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    // TMA path only: K a multiple of 16, N a multiple of 8, 16-byte aligned operands
+    if (K % 16 != 0 || N % 8 != 0 || !aligned16(A) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(out))
+        return kBadShape;
+    return launch_dense<256, 2>(A, Wg, act_scale, wg_scale, bg, out, M, K, N, stream, Wu, wu_scale, bu);
 }
 
 }  // namespace fb200

@@ -14,6 +14,13 @@ int dense_gemm_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K,
 int dense_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream, int force_bn);
 
+// out (M,N) fp16 = fp16(SiLU(g) * u), g = (act_scale*wg_scale)*acc_g + bg, u likewise from Wu: the
+// gate and up projections of a gated MLP in one GEMM pass. Wg, Wu (N,K) s8; bg / bu may be null.
+// Needs K % 16 == 0, N % 8 == 0 and 16-byte aligned A, Wg, Wu, out (else kBadShape).
+int dense_gemm_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                     const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,
+                     int M, int K, int N, cudaStream_t stream);
+
 // Address of this device's status word (a file-scope __device__ int); nullptr on failure.
 int* status_word();
 // Reads the status word back (synchronising copy); clears it when reset != 0. -1 on failure.

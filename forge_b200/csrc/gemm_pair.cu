@@ -337,7 +337,9 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 // [128r, 128r+128) with their metadata, and token rows [r*BT/2, (r+1)*BT/2) of the tile; its
 // TMEM receives weight rows [128r, 128r+128) x BT token columns.
 
-template <int BT>
+constexpr int kXbufBytes = 4 * 32 * 32 * (int)sizeof(float);   // gated epilogue: 4 warp pairs x 4 KB
+
+template <int BT, int EPI = 0>
 struct SparsePairCfg {
     static constexpr int HT = BT / 2;                       // tokens staged per CTA
     static constexpr int kABytes = 128 * 128;
@@ -345,7 +347,7 @@ struct SparsePairCfg {
     static constexpr int kMetaBytes = 128 * 32;
     static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
     static constexpr int kBarBytes = 256;
-    static constexpr int kFixed = kBarBytes;
+    static constexpr int kFixed = kBarBytes + (EPI == 2 ? kXbufBytes : 0);
     static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
@@ -362,14 +364,21 @@ struct SparsePairCfg {
 template <int BT, int EPI>
 __global__ void __launch_bounds__(kSpThreads, 1)
 sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const __grid_constant__ CUtensorMap tm_meta, void* __restrict__ out,
+                   const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
+                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
-                   const __half* __restrict__ bias, int M, int N_out, int K, int* __restrict__ status) {
-    using Cfg = SparsePairCfg<BT>;
+                   const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
+                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
+    // EPI 2 (gated): each CTA's 128-row weight tile is 64 gate rows followed by the 64 up rows of the
+    // same output columns, so a pair produces 128 output columns per tile.
+    using Cfg = SparsePairCfg<BT, EPI>;
     constexpr int HT = Cfg::HT;
+    constexpr int CTA_W = (EPI == 2) ? 64 : 128;   // output columns per CTA
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* smem_stage = smem;
-    const PairBars bars = carve_bars(smem + Cfg::kStages * Cfg::kStageBytes, Cfg::kStages);
+    float* smem_xbuf = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    const PairBars bars =
+        carve_bars(smem + Cfg::kStages * Cfg::kStageBytes + (EPI == 2 ? kXbufBytes : 0), Cfg::kStages);
 
     const int warp_id = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -380,7 +389,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         return;
     }
 
-    const int w_blocks = (N_out + 255) / 256;
+    const int w_blocks = (N_out + 2 * CTA_W - 1) / (2 * CTA_W);
     const int t_blocks = (M + BT - 1) / BT;
     const int num_tiles = w_blocks * t_blocks;
     const int num_kb = (K + 255) / 256;
@@ -412,7 +421,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             bool ok = true;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
-                const int w_row = tc.a_blk * 256 + (int)rank * 128;
+                const int w_row = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W;
                 const int t_row = tc.b_blk * BT + (int)rank * HT;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
@@ -425,10 +434,20 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
                     if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
                     const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
-                    tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
+                    if (EPI == 2) {
+                        tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
+                        tma_load_2d_pair(sa + Cfg::kABytes / 2, &tm_w2, full_leader, kb * 128, w_row);
+#pragma unroll
+                        for (int c = 0; c < 2; c++) {
+                            tma_load_3d_pair(sm + c * 2048, &tm_meta, full_leader, 0, w_row, kb * 2 + c);
+                            tma_load_3d_pair(sm + c * 2048 + 1024, &tm_meta2, full_leader, 0, w_row, kb * 2 + c);
+                        }
+                    } else {
+                        tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
+                        tma_load_3d_pair(sm, &tm_meta, full_leader, 0, w_row, kb * 2);
+                    }
                     tma_load_2d_pair(sb, &tm_x, full_leader, kb * 256, t_row);
                     tma_load_2d_pair(sb + Cfg::kBAtomBytes, &tm_x, full_leader, kb * 256 + 128, t_row);
-                    tma_load_3d_pair(sm, &tm_meta, full_leader, 0, w_row, kb * 2);
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -494,37 +513,83 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int chunk0 = (warp_id - 2) >> 2;
         const bool has_bias = (bias != nullptr);
         int local = 0;
-        for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
-            const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
-            const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
-            const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
-            const int n = tc.a_blk * 256 + (int)rank * 128 + q * 32 + lane;
-            const int m0 = tc.b_blk * BT;
-            float ws = 0.f, bs = 0.f;
-            if (EPI == 1 && n < N_out) {
-                ws = __half2float(w_scale[n]);
-                if (has_bias) bs = __half2float(bias[n]);
-            }
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag))) {
-                atomicExch(status, 404);
-                break;
-            }
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+        if (EPI == 2) {
+            const bool is_gate = q < 2;
+            const int pair = (q & 1) + 2 * chunk0;
+            float* xbuf = smem_xbuf + pair * 1024;
+            const __half* my_scale = is_gate ? w_scale : w_scale2;
+            const __half* my_bias = is_gate ? bias : bias2;
+            bool ok = true;   // after a failed wait: keep meeting the partner warp at the barriers
+            for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W + (q & 1) * 32 + lane;
+                const int m0 = tc.b_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (n < N_out) {
+                    ws = __half2float(my_scale[n]);
+                    if (my_bias != nullptr) bs = __half2float(my_bias[n]);
+                }
+                if (ok) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag));
+                    if (!ok) atomicExch(status, 404);
+                }
+                if (ok) tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
 #pragma unroll 1
-            for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
-                const int m_first = m0 + c * 32;
-                if (m_first >= M) break;
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, v);
-                float as_lane = 0.f;
-                if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
-                tmem_ld_wait();
-                store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M) break;
+                    uint32_t v[32];
+                    float as_lane = 0.f;
+                    if (ok) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                        if (m_first + lane < M) as_lane = act_scale[m_first + lane];
+                        tmem_ld_wait();
+                    }
+                    gated_chunk(is_gate, ok, v, xbuf, 4 + pair, static_cast<__half*>(out), N_out, M, n, m_first,
+                                as_lane, ws, bs, my_bias != nullptr);
+                }
+                if (ok) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+        } else {
+            for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n = tc.a_blk * 256 + (int)rank * 128 + q * 32 + lane;
+                const int m0 = tc.b_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (EPI == 1 && n < N_out) {
+                    ws = __half2float(w_scale[n]);
+                    if (has_bias) bs = __half2float(bias[n]);
+                }
+                if (!__all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag))) {
+                    atomicExch(status, 404);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+                for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    float as_lane = 0.f;
+                    if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
+                    tmem_ld_wait();
+                    store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+            }
         }
     }
 
@@ -621,15 +686,20 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
 template <int BT, int EPI>
 int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
                        const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
-                       cudaStream_t stream) {
-    using Cfg = SparsePairCfg<BT>;
+                       cudaStream_t stream, const int8_t* W_comp2 = nullptr, const uint32_t* w_meta2 = nullptr,
+                       const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
+    using Cfg = SparsePairCfg<BT, EPI>;
+    constexpr int CTA_W = (EPI == 2) ? 64 : 128;
     static int max_pairs[64] = {};
-    CUtensorMap tm_w, tm_x, tm_meta;
+    CUtensorMap tm_w, tm_x, tm_meta, tm_w2, tm_meta2;
     {
         const uint64_t dims[2] = {(uint64_t)K / 2, (uint64_t)N_out};
         const uint64_t str[1] = {(uint64_t)K / 2};
-        const uint32_t box[2] = {128, 128};
+        const uint32_t box[2] = {128, (uint32_t)CTA_W};
         if (!make_tmap(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W_comp, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+        if (!make_tmap(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (EPI == 2) ? W_comp2 : W_comp, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
     }
     {
@@ -642,16 +712,19 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     {
         const uint64_t dims[3] = {4, (uint64_t)N_out, (uint64_t)K / 128};
         const uint64_t str[2] = {(uint64_t)K / 8, 16};
-        const uint32_t box[3] = {4, 128, 2};
+        const uint32_t box[3] = {4, (uint32_t)CTA_W, (uint32_t)((EPI == 2) ? 1 : 2)};
         if (!make_tmap(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w_meta, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return kLaunchFailed;
+        if (!make_tmap(&tm_meta2, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (EPI == 2) ? w_meta2 : w_meta, dims, str, box,
                        CU_TENSOR_MAP_SWIZZLE_NONE))
             return kLaunchFailed;
     }
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
-    const long long tiles = (long long)((N_out + 255) / 256) * ((M + BT - 1) / BT);
-    return launch_pairs(sparse_pair_kernel<BT, EPI>, kSpThreads, Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x, tm_meta,
-                        out, act_scale, w_scale, bias, M, N_out, K, status);
+    const long long tiles = (long long)((N_out + 2 * CTA_W - 1) / (2 * CTA_W)) * ((M + BT - 1) / BT);
+    return launch_pairs(sparse_pair_kernel<BT, EPI>, kSpThreads, Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
+                        tm_meta, tm_w2, tm_meta2, out, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, status);
 }
 
 template <int EPI>
@@ -686,6 +759,20 @@ int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int bt) {
     return sparse_pair_dispatch<1>(bt, W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+}
+
+int sparse_pair_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,
+                      const int8_t* x, const float* act_scale, const __half* wg_scale, const __half* wu_scale,
+                      const __half* bg, const __half* bu, __half* out, int M, int K, int N_out, cudaStream_t stream,
+                      int bt) {
+    switch (bt) {
+    case 128: return launch_sparse_pair<128, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                                Wu_comp, wu_meta, wu_scale, bu);
+    case 192: return launch_sparse_pair<192, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                                Wu_comp, wu_meta, wu_scale, bu);
+    default:  return launch_sparse_pair<224, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                                Wu_comp, wu_meta, wu_scale, bu);
+    }
 }
 
 }  // namespace fb200

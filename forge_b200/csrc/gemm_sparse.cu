@@ -39,14 +39,16 @@ constexpr int kEpiWarps = 8;             // two warps per TMEM lane quarter, alt
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kMetaBytes = BW * 32;        // 128 rows x 32 bytes per slab
 
-template <int BT>
+constexpr int kXbufBytes = 4 * 32 * 32 * (int)sizeof(float);   // gated epilogue: 4 warp pairs x 4 KB
+
+template <int BT, int EPI = 0>
 struct SparseCfg {
     static constexpr int kABytes = BW * 128;
     static constexpr int kBAtomBytes = BT * 128;
     static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
     static constexpr int kAccBufs = (2 * BT + 32 <= 512) ? 2 : 1;
     static constexpr int kBarBytes = 256;
-    static constexpr int kFixed = kBarBytes;
+    static constexpr int kFixed = kBarBytes + (EPI == 2 ? kXbufBytes : 0);
     static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesMax > 8 ? 8 : kStagesMax;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
@@ -78,18 +80,26 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int w_blocks, int t_block
     return c;
 }
 
-// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias).
+// EPI: 0 = raw s32 output, 1 = fp16 dequant (+ optional bias),
+//      2 = gated: the 128-row weight tile is 64 rows of a gate weight (tm_w / tm_meta) followed by
+//          the same 64 rows of an up weight (tm_w2 / tm_meta2); output = fp16(SiLU(g) * u), 64
+//          output columns per tile.
 template <int BT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const __grid_constant__ CUtensorMap tm_meta, void* __restrict__ out,
+                   const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
+                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
-                   const __half* __restrict__ bias, int M, int N_out, int K, int* __restrict__ status) {
-    using Cfg = SparseCfg<BT>;
+                   const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
+                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
+    using Cfg = SparseCfg<BT, EPI>;
+    constexpr int TILE_W = (EPI == 2) ? BW / 2 : BW;   // output columns per tile
     extern __shared__ __align__(1024) uint8_t smem[];
 
     uint8_t* smem_stage = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    float* smem_xbuf = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes +
+                                                 (EPI == 2 ? kXbufBytes : 0));
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + Cfg::kStages;
     uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -105,7 +115,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         return;
     }
 
-    const int w_blocks = (N_out + BW - 1) / BW;
+    const int w_blocks = (N_out + TILE_W - 1) / TILE_W;
     const int t_blocks = (M + BT - 1) / BT;
     const int num_tiles = w_blocks * t_blocks;
     const int num_kb = (K + SLAB_K - 1) / SLAB_K;
@@ -155,10 +165,22 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     uint8_t* sb = sa + Cfg::kABytes;
                     uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-                    tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), tc.w_blk * BW);
+                    if (EPI == 2) {
+                        // 64 gate rows then 64 up rows; metadata per 16-byte column: [gate 64 rows][up 64 rows]
+                        const int w_row = tc.w_blk * TILE_W;
+                        tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), w_row);
+                        tma_load_2d(sa + Cfg::kABytes / 2, &tm_w2, &full_bar[stage], kb * (SLAB_K / 2), w_row);
+#pragma unroll
+                        for (int c = 0; c < 2; c++) {
+                            tma_load_3d(sm + c * 2048, &tm_meta, &full_bar[stage], 0, w_row, kb * 2 + c);
+                            tma_load_3d(sm + c * 2048 + 1024, &tm_meta2, &full_bar[stage], 0, w_row, kb * 2 + c);
+                        }
+                    } else {
+                        tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), tc.w_blk * BW);
+                        tma_load_3d(sm, &tm_meta, &full_bar[stage], 0, tc.w_blk * BW, kb * 2);
+                    }
                     tma_load_2d(sb, &tm_x, &full_bar[stage], kb * SLAB_K, tc.t_blk * BT);
                     tma_load_2d(sb + Cfg::kBAtomBytes, &tm_x, &full_bar[stage], kb * SLAB_K + 128, tc.t_blk * BT);
-                    tma_load_3d(sm, &tm_meta, &full_bar[stage], 0, tc.w_blk * BW, kb * 2);
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -222,38 +244,85 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int chunk0 = (warp_id - 2) >> 2;     // 0 or 1: which alternate chunks this warp takes
         const bool has_bias = (bias != nullptr);
         int local = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
-            const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
-            const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
-            const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
-            const int n = tc.w_blk * BW + q * 32 + lane;   // this thread's weight row = output column
-            const int m0 = tc.t_blk * BT;
-            float ws = 0.f, bs = 0.f;
-            if (EPI == 1 && n < N_out) {
-                ws = __half2float(w_scale[n]);
-                if (has_bias) bs = __half2float(bias[n]);
-            }
-            // warp-uniform outcome: the TMEM loads below are .sync.aligned
-            if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag))) {
-                atomicExch(status, 204);
-                break;
-            }
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+        if (EPI == 2) {
+            // lanes 0-63 hold gate rows, lanes 64-127 the up rows of the same output columns
+            const bool is_gate = q < 2;
+            const int pair = (q & 1) + 2 * chunk0;
+            float* xbuf = smem_xbuf + pair * 1024;
+            const __half* my_scale = is_gate ? w_scale : w_scale2;
+            const __half* my_bias = is_gate ? bias : bias2;
+            bool ok = true;   // after a failed wait: keep meeting the partner warp at the barriers
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n = tc.w_blk * TILE_W + (q & 1) * 32 + lane;
+                const int m0 = tc.t_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (n < N_out) {
+                    ws = __half2float(my_scale[n]);
+                    if (my_bias != nullptr) bs = __half2float(my_bias[n]);
+                }
+                if (ok) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag));
+                    if (!ok) atomicExch(status, 204);
+                }
+                if (ok) tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
 #pragma unroll 1
-            for (int c = chunk0; c < BT / 32; c += kEpiWarps / 4) {
-                const int m_first = m0 + c * 32;
-                if (m_first >= M) break;   // warp-uniform: the rest of the tile is past the last token
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, v);
-                float as_lane = 0.f;
-                if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
-                tmem_ld_wait();
-                store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                for (int c = chunk0; c < BT / 32; c += kEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M) break;
+                    uint32_t v[32];
+                    float as_lane = 0.f;
+                    if (ok) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                        if (m_first + lane < M) as_lane = act_scale[m_first + lane];
+                        tmem_ld_wait();
+                    }
+                    gated_chunk(is_gate, ok, v, xbuf, 4 + pair, static_cast<__half*>(out), N_out, M, n, m_first,
+                                as_lane, ws, bs, my_bias != nullptr);
+                }
+                if (ok) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        } else {
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n = tc.w_blk * BW + q * 32 + lane;   // this thread's weight row = output column
+                const int m0 = tc.t_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (EPI == 1 && n < N_out) {
+                    ws = __half2float(w_scale[n]);
+                    if (has_bias) bs = __half2float(bias[n]);
+                }
+                // warp-uniform outcome: the TMEM loads below are .sync.aligned
+                if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], acc_phase, abort_flag))) {
+                    atomicExch(status, 204);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+                for (int c = chunk0; c < BT / 32; c += kEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M) break;   // warp-uniform: the rest of the tile is past the last token
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    float as_lane = 0.f;
+                    if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
+                    tmem_ld_wait();
+                    store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            }
         }
     }
 
@@ -300,8 +369,10 @@ __global__ void sparse_gemm_ragged_kernel(const int8_t* __restrict__ W_comp, con
 template <int BT, int EPI>
 int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
                   const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
-                  cudaStream_t stream) {
-    using Cfg = SparseCfg<BT>;
+                  cudaStream_t stream, const int8_t* W_comp2 = nullptr, const uint32_t* w_meta2 = nullptr,
+                  const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
+    using Cfg = SparseCfg<BT, EPI>;
+    constexpr int TILE_W = (EPI == 2) ? BW / 2 : BW;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -311,12 +382,15 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
             return kLaunchFailed;
         attr_set[dev & 63] = true;
     }
-    CUtensorMap tm_w, tm_x, tm_meta;
+    CUtensorMap tm_w, tm_x, tm_meta, tm_w2, tm_meta2;
     {
         const uint64_t dims[2] = {(uint64_t)K / 2, (uint64_t)N_out};
         const uint64_t str[1] = {(uint64_t)K / 2};
-        const uint32_t box[2] = {128, BW};
+        const uint32_t box[2] = {128, TILE_W};
         if (!make_tmap(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W_comp, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+        if (!make_tmap(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (EPI == 2) ? W_comp2 : W_comp, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
     }
     {
@@ -327,20 +401,24 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
             return kLaunchFailed;
     }
     {
-        // (4 words, N_out rows, K/128 column groups): one box = 2 column groups of 128 rows x 16 bytes
+        // (4 words, N_out rows, K/128 column groups). Plain: one box = 2 column groups of 128 rows x 16
+        // bytes. Gated: one box = 1 column group of 64 rows (gate and up halves are placed separately).
         const uint64_t dims[3] = {4, (uint64_t)N_out, (uint64_t)K / 128};
         const uint64_t str[2] = {(uint64_t)K / 8, 16};
-        const uint32_t box[3] = {4, BW, 2};
+        const uint32_t box[3] = {4, (uint32_t)TILE_W, (uint32_t)((EPI == 2) ? 1 : 2)};
         if (!make_tmap(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w_meta, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return kLaunchFailed;
+        if (!make_tmap(&tm_meta2, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (EPI == 2) ? w_meta2 : w_meta, dims, str, box,
                        CU_TENSOR_MAP_SWIZZLE_NONE))
             return kLaunchFailed;
     }
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
-    const long long tiles = (long long)((N_out + BW - 1) / BW) * ((M + BT - 1) / BT);
+    const long long tiles = (long long)((N_out + TILE_W - 1) / TILE_W) * ((M + BT - 1) / BT);
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, out, act_scale, w_scale, bias, M,
-                                                      N_out, K, status);
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_w2, tm_meta2, out, act_scale, w_scale,
+                                                      bias, w_scale2, bias2, M, N_out, K, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -403,6 +481,40 @@ int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int force_bt) {
     return sparse_dispatch<1>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream, force_bt);
+}
+
+int sparse_gemm_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,
+                      const int8_t* x, const float* act_scale, const __half* wg_scale, const __half* wu_scale,
+                      const __half* bg, const __half* bu, __half* out, int M, int K, int N_out, cudaStream_t stream,
+                      int force_bt) {
+    if (M <= 0 || K <= 0 || N_out <= 0) return kOk;
+    if (Wg_comp == nullptr || wg_meta == nullptr || Wu_comp == nullptr || wu_meta == nullptr || x == nullptr ||
+        act_scale == nullptr || wg_scale == nullptr || wu_scale == nullptr || out == nullptr)
+        return kBadPointer;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    // TMA path only: K a multiple of 128, 16-byte aligned operands
+    if (K % 128 != 0 || !aligned16(Wg_comp) || !aligned16(Wu_comp) || !aligned16(wg_meta) || !aligned16(wu_meta) ||
+        !aligned16(x))
+        return kBadShape;
+    if (force_bt == 0 && M >= 1024 && N_out >= 256) {
+        const int r = sparse_pair_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, x, act_scale, wg_scale, wu_scale, bg, bu,
+                                        out, M, K, N_out, stream, 224);
+        if (r >= 0) return r;
+    }
+    if (force_bt > 1000) {
+        const int r = sparse_pair_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, x, act_scale, wg_scale, wu_scale, bg, bu,
+                                        out, M, K, N_out, stream, force_bt - 1000);
+        if (r >= 0) return r;
+    }
+    const int bt = (force_bt == 32 || force_bt == 64 || force_bt == 128) ? force_bt : (M > 64 ? 128 : (M > 32 ? 64 : 32));
+    switch (bt) {
+    case 128: return launch_sparse<128, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                           Wu_comp, wu_meta, wu_scale, bu);
+    case 64:  return launch_sparse<64, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                          Wu_comp, wu_meta, wu_scale, bu);
+    default:  return launch_sparse<32, 2>(Wg_comp, x, wg_meta, act_scale, wg_scale, bg, out, M, K, N_out, stream,
+                                          Wu_comp, wu_meta, wu_scale, bu);
+    }
 }
 
 }  // namespace fb200

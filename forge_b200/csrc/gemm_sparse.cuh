@@ -16,4 +16,11 @@ int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int force_bt);
 
+// out (M,N_out) fp16 = fp16(SiLU(g) * u): gate and up projections (both 2:4 sparse, N_out rows
+// each) of a gated MLP in one pass. Needs K % 128 == 0 and 16-byte aligned operands (kBadShape).
+int sparse_gemm_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,
+                      const int8_t* x, const float* act_scale, const __half* wg_scale, const __half* wu_scale,
+                      const __half* bg, const __half* bu, __half* out, int M, int K, int N_out, cudaStream_t stream,
+                      int force_bt);
+
 }  // namespace fb200

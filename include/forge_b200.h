@@ -142,6 +142,41 @@ int forge_splitk_reduce(const float* workspace, const void* bias, void* output, 
 int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta, int32_t* output,
                                int M, int K, int N_out, forge_stream_t stream);
 
+/* ---------------------------------------------------------------- gated MLP (additive) */
+
+/* No counterpart in the reference (its only "gating" is an FP32 training op, src/nn/gating.cu).
+ * Gate and up projections of a Llama-style MLP in one GEMM pass with the activation fused in
+ * the epilogue: h[m,n] = fp16(SiLU(g) * u), g = (act_scale[m]*wg_scale[n]) * sum_k x[m,k]Wg[n,k] + bg[n],
+ * u likewise from Wu; g, u and SiLU(g) = g / (1 + exp(-g)) are evaluated in fp32 and h is rounded
+ * once. x_int8 (M,K), Wg / Wu (N,K) int8; bg / bu may be NULL. Needs K % 16 == 0, N % 8 == 0 and
+ * 16-byte aligned operands (FORGE_B200_BAD_SHAPE otherwise). */
+int forge_int8_gated_gemm(const int8_t* x_int8, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                          const void* wg_scale, const void* wu_scale, const void* bg, const void* bu, void* h_out,
+                          int M, int K, int N, forge_stream_t stream);
+
+/* The same with 2:4-sparse gate and up weights (compressed values + packed metadata as produced
+ * by forge_prune_compress_24 / forge_pack_metadata). Needs K % 128 == 0. */
+int forge_sparse_int8_gated_gemm(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp,
+                                 const uint32_t* wu_meta, const int8_t* x_int8, const float* act_scale,
+                                 const void* wg_scale, const void* wu_scale, const void* bg, const void* bu,
+                                 void* h_out, int M, int K, int N_out, forge_stream_t stream);
+
+/* Whole W8A8 gated MLP block: per-token quantize(x) -> gated GEMM -> per-token quantize(h) ->
+ * down GEMM + dequant (+ bd). x (M,d_model) fp16 -> out (M,d_model) fp16. Wg / Wu (d_ffn,d_model),
+ * Wd (d_model,d_ffn) int8 with fp16 per-channel scales. `workspace` is caller-owned device memory of
+ * forge_w8a8_gated_mlp_workspace_bytes(M, d_model, d_ffn) bytes, 256-byte aligned; on return it
+ * holds, in this order (each block padded to 256 bytes): int8 x (M*d_model), fp32 x scales (M),
+ * fp16 h (M*d_ffn), int8 h (M*d_ffn), fp32 h scales (M). */
+unsigned long long forge_w8a8_gated_mlp_workspace_bytes(int M, int d_model, int d_ffn);
+int forge_w8a8_gated_mlp(const void* x, const int8_t* Wg, const int8_t* Wu, const int8_t* Wd, const void* wg_scale,
+                         const void* wu_scale, const void* wd_scale, const void* bg, const void* bu, const void* bd,
+                         void* out, int M, int d_model, int d_ffn, void* workspace, forge_stream_t stream);
+int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp,
+                                const uint32_t* wu_meta, const int8_t* Wd_comp, const uint32_t* wd_meta,
+                                const void* wg_scale, const void* wu_scale, const void* wd_scale, const void* bg,
+                                const void* bu, const void* bd, void* out, int M, int d_model, int d_ffn,
+                                void* workspace, forge_stream_t stream);
+
 /* ---------------------------------------------------------------- forge::sparsity */
 
 /* forge::sparsity::prune_compress_24 - include/forge/sparsity/prune_compress.cuh:23-30,

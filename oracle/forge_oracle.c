@@ -161,6 +161,29 @@ void oracle_dequantize_gemm_epilogue(const int32_t* acc, const float* act_scale,
     }
 }
 
+/* ---- gated epilogue (no reference counterpart; the composition this library defines):
+ * g = fma.rn.ftz(f32(acc_g), mul.ftz(act_scale, wg_scale), bg) and u likewise, both fp32 and
+ * bit-reproducible here; h = SiLU(g) * u with SiLU(x) = x / (1 + exp(-x))
+ * (include/forge/primitives/activation.cuh:66-69) evaluated in double; one rounding to fp16.
+ * The GPU evaluates SiLU in fp32 with approximate exp/divide, so it is compared to this within
+ * 1 fp16 ulp, not bit-exactly. ---- */
+void oracle_gated_epilogue(const int32_t* acc_g, const int32_t* acc_u, const float* act_scale,
+                           const uint16_t* wg_scale, const uint16_t* wu_scale, const uint16_t* bg, const uint16_t* bu,
+                           uint16_t* out, int M, int N) {
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; m++) {
+        for (int n = 0; n < N; n++) {
+            const float sg = mul_ftz(act_scale[m], half_to_float(wg_scale[n]));
+            const float su = mul_ftz(act_scale[m], half_to_float(wu_scale[n]));
+            const float ag = (float)acc_g[(size_t)m * N + n], au = (float)acc_u[(size_t)m * N + n];
+            const float g = bg ? fma_ftz(ag, sg, half_to_float(bg[n])) : mul_ftz(ag, sg);
+            const float u = bu ? fma_ftz(au, su, half_to_float(bu[n])) : mul_ftz(au, su);
+            const double h = ((double)g / (1.0 + exp(-(double)g))) * (double)u;
+            out[(size_t)m * N + n] = float_to_half((float)h);
+        }
+    }
+}
+
 /* ---- 2:4 prune decision for one group; src/sparsity/prune_compress.cu:33-59 ---- */
 static void prune_group(const int8_t* v, int* keep0, int* keep1) {
     int a[4];

@@ -29,6 +29,7 @@ def oracle():
         lib.oracle_quantize.argtypes = [_vp, _vp, _vp, _i, _i]
         lib.oracle_dequantize_bias.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i]
         lib.oracle_dequantize_gemm_epilogue.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i]
+        lib.oracle_gated_epilogue.argtypes = [_vp] * 8 + [_i, _i]
         lib.oracle_prune_compress_24.argtypes = [_vp, _vp, _vp, _i, _i]
         lib.oracle_prune_24_dense.argtypes = [_vp, _vp, _i, _i]
         lib.oracle_pack_metadata.argtypes = [_vp, _vp, _i, _i]
@@ -78,6 +79,26 @@ def dequantize_bias(acc, act_scale, w_scale, bias, gemm_epilogue=False):
     fn = oracle().oracle_dequantize_gemm_epilogue if gemm_epilogue else oracle().oracle_dequantize_bias
     fn(_p(acc), _p(act_scale), _p(w_scale), _p(bias), _p(out), M, N)
     return out
+
+
+def gated_epilogue(acc_g, acc_u, act_scale, wg_scale, wu_scale, bg, bu):
+    acc_g, acc_u = _c(acc_g, np.int32), _c(acc_u, np.int32)
+    act_scale, wg_scale, wu_scale = _c(act_scale, np.float32), _c(wg_scale, np.float16), _c(wu_scale, np.float16)
+    bg = None if bg is None else _c(bg, np.float16)
+    bu = None if bu is None else _c(bu, np.float16)
+    M, N = acc_g.shape
+    out = np.empty((M, N), np.float16)
+    oracle().oracle_gated_epilogue(_p(acc_g), _p(acc_u), _p(act_scale), _p(wg_scale), _p(wu_scale), _p(bg), _p(bu),
+                                   _p(out), M, N)
+    return out
+
+
+def half_ulp_distance(a, b):
+    """Element-wise distance in fp16 units of least precision between two float16 arrays."""
+    def ordered(x):
+        u = x.view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, 0x8000 - u, u)
+    return np.abs(ordered(np.ascontiguousarray(a)) - ordered(np.ascontiguousarray(b)))
 
 
 def prune_compress_24(w):
