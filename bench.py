@@ -363,6 +363,39 @@ def run_case(args):
             fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, s)
             work = 0.375 * n * k / 1e9
         unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
+    elif name in ("mlp", "mlp_sparse"):
+        # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
+        m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
+        x = torch.randn((m, dm), generator=g, device=dev, dtype=torch.float16)
+
+        def qweight(rows, cols):
+            w = torch.randn((rows, cols), generator=g, device=dev) * 0.02
+            sc = w.abs().amax(dim=1).clamp(min=1e-8) / 127.0
+            wq = torch.clamp(torch.round(w / sc[:, None]), -127, 127).to(torch.int8)
+            return wq, sc.to(torch.float16)
+
+        (Wg, sg), (Wu, su), (Wd, sd) = qweight(df, dm), qweight(df, dm), qweight(dm, df)
+        outp = torch.empty((m, dm), dtype=torch.float16, device=dev)
+        ws = torch.empty(lib.forge_w8a8_gated_mlp_workspace_bytes(m, dm, df), dtype=torch.uint8, device=dev)
+        if name == "mlp":
+            fn = lambda: lib.forge_w8a8_gated_mlp(x.data_ptr(), Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(),
+                                                  sg.data_ptr(), su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(),
+                                                  m, dm, df, ws.data_ptr(), s)
+        else:
+            packs = []
+            for W in (Wg, Wu, Wd):
+                n_, k_ = W.shape
+                comp = torch.empty((n_, k_ // 2), dtype=torch.int8, device=dev)
+                raw = torch.empty((n_ * (k_ // 4),), dtype=torch.uint8, device=dev)
+                meta = torch.empty((n_, k_ // 32), dtype=torch.int32, device=dev)
+                C.prune_compress_24(W, comp, raw, n_, k_)
+                C.pack_metadata(raw, meta, n_, k_)
+                packs += [comp, meta]
+            fn = lambda: lib.forge_sparse_w8a8_gated_mlp(x.data_ptr(), *[t.data_ptr() for t in packs], sg.data_ptr(),
+                                                         su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(), m, dm,
+                                                         df, ws.data_ptr(), s)
+        work, unit, bound = 3 * 2.0 * m * dm * df / 1e12, "TOP/s", "tensor"
+        shape = {"tokens": m, "d_model": dm, "d_ffn": df}
     else:
         raise SystemExit(f"unknown case {name}")
 
@@ -384,9 +417,81 @@ def run_case(args):
     ms = statistics.median(times)
     achieved = work / (ms * 1e-3)
     peak = 2.0 * peaks["bf16_burst"] if bound == "tensor" else peaks["hbm"]
-    print(json.dumps({"case": name, "shape": shape, "ms": ms, "ms_min": min(times), "achieved": achieved, "unit": unit,
+    extra = {"tokens_per_s": shape["tokens"] / (ms * 1e-3)} if name.startswith("mlp") else {}
+    print(json.dumps({"case": name, "shape": shape, **extra, "ms": ms, "ms_min": min(times), "achieved": achieved,
+                      "unit": unit,
                       "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
                       "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps}))
+
+
+def run_sharded_case(args):
+    """BASELINE config 5: 2:4-sparse W8A8 linear, M tokens x K -> N, sharded over the ranks of a
+    torchrun launch. --case shard_rows: token rows split, no collective. --case shard_cols: output
+    channels split, FP16 all-gather over NVLink. Prints one JSON line from rank 0 (device time,
+    max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from forge_b200 import _forge_C as C
+    from forge_b200.sharded import ShardedSparseLinear, SparseWeights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m, k, n = args.m or 65536, args.k or 8192, args.n or 28672
+    g = torch.Generator(device=dev)
+    g.manual_seed(55)   # replicated weights: same seed on every rank
+    W = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8, device=dev)
+    comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+    raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+    meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+    C.prune_compress_24(W, comp, raw, n, k)
+    C.pack_metadata(raw, meta, n, k)
+    del W, raw
+    w = SparseWeights(comp, meta, (torch.rand(n, generator=g, device=dev) * 0.01 + 0.001).half(), None)
+    mode = "rows" if args.case == "shard_rows" else "columns"
+    layer = ShardedSparseLinear(w, mode, chunks=8)
+    if mode == "rows":
+        r0, rows = layer.rows_of(m)
+        g.manual_seed(1000 + rank)
+        x = torch.randn((rows, k), generator=g, device=dev, dtype=torch.float16)
+    else:
+        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)   # replicated activations
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 1)):
+        y = layer(x)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = layer(x)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        line = {"case": args.case, "n_gpus": world, "shape": {"M": m, "K": k, "N": n}, "ms": ms,
+                "tokens_per_s": m / (ms * 1e-3), "dense_equiv_tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+                "includes": "per-token quantize + 2:4-sparse GEMM + dequant" + (" + FP16 all-gather" if mode == "columns" else ""),
+                "steps": args.steps}
+        if mode == "columns" and world > 1:
+            recv = (world - 1) / world * 2.0 * m * n
+            line["allgather_bytes_received_per_gpu"] = recv
+            line["link_bound_ms_at_770GBs"] = recv / 770e9 * 1e3
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -397,12 +502,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="headline",
                     help="headline (the contract line) or one kernel: dense, dense_s32, sparse, sparse_s32, "
-                         "quantize, dequant, prune, pack")
+                         "quantize, dequant, prune, pack, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn)")
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
     ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")
     args = ap.parse_args()
+    if args.case in ("shard_rows", "shard_cols"):
+        run_sharded_case(args)
+        return
     if args.case != "headline":
         run_case(args)
         return

@@ -1,0 +1,126 @@
+"""Multi-GPU sharding of the W8A8 linear layers: one process per GPU (torchrun), NCCL for the
+one exchange step that exists.
+
+The reference is single-GPU (no NCCL, MPI or peer access anywhere in its tree); this module is
+the additive layer BASELINE config 5 asks for. Two modes, both bit-identical to the single-GPU
+result because every output element is still one exact int32 accumulation followed by the same
+fp32 epilogue:
+
+  rows     token rows are split across ranks, weights replicated. No communication at all: each
+           rank quantizes and multiplies its own rows. This is the mode that scales linearly.
+  columns  output channels (weight rows) are split across ranks, activations replicated; each
+           rank computes out[:, n0:n1] and the FP16 slices are all-gathered over NVLink. The
+           gather moves (g-1)/g * 2*M*N bytes into every GPU, so it is link-bound, not
+           compute-bound; rows are processed in chunks so the gather of chunk i overlaps the
+           GEMM of chunk i+1, and the column interleave is a copy out of the gather buffer.
+
+The local compute is the C ABI of libforge_b200 (no fallback). `local_linear` can be injected so
+that the partition / gather / interleave logic is testable with gloo on CPUs.
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def partition(total, world, rank):
+    """Balanced contiguous partition of `total` items: (start, count) of `rank`'s share."""
+    base, extra = divmod(total, world)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+@dataclass
+class SparseWeights:
+    """One 2:4-sparse INT8 weight: compressed values (N, K/2) int8, metadata (N, K/32) int32,
+    fp16 per-channel scales (N) and optional fp16 bias (N) - the buffers of the reference's
+    SparseLinear module (python/forge/nn/linear.py:207-217)."""
+    W_comp: torch.Tensor
+    w_meta: torch.Tensor
+    w_scale: torch.Tensor
+    bias: torch.Tensor = None
+
+    def rows(self, start, count):
+        b = None if self.bias is None else self.bias[start:start + count]
+        return SparseWeights(self.W_comp[start:start + count], self.w_meta[start:start + count],
+                             self.w_scale[start:start + count], b)
+
+
+def _forge_sparse_linear(x, w):
+    """x (m, K) fp16 on this rank's GPU -> (m, n) fp16 through libforge_b200."""
+    from . import _forge_C as C
+    m, k = x.shape
+    scratch_q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+    scratch_s = torch.empty((m,), dtype=torch.float32, device=x.device)
+    return C.sparse_int8_linear(x, w.W_comp, w.w_meta, w.w_scale, w.bias, scratch_q, scratch_s)
+
+
+class ShardedSparseLinear:
+    """2:4-sparse W8A8 linear layer sharded over the ranks of `group`.
+
+    mode "rows":    `weights` is the full weight on every rank; forward(x_local) takes this
+                    rank's token rows and returns their outputs (no collective).
+    mode "columns": `weights` is the full weight; the constructor keeps only this rank's output
+                    channels. forward(x) takes all tokens (replicated) and returns the full
+                    (M, N) output on every rank.
+    """
+
+    def __init__(self, weights, mode, group=None, chunks=4, local_linear=None):
+        if mode not in ("rows", "columns"):
+            raise ValueError("mode must be 'rows' or 'columns'")
+        self.mode = mode
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.chunks = max(1, chunks)
+        self.local_linear = local_linear or _forge_sparse_linear
+        self.N = weights.W_comp.shape[0]
+        if mode == "columns":
+            if self.N % self.world != 0:
+                raise ValueError(f"output channels ({self.N}) must divide evenly over {self.world} ranks")
+            n0, n = partition(self.N, self.world, self.rank)
+            self.weights = weights.rows(n0, n)
+        else:
+            self.weights = weights
+
+    def rows_of(self, M):
+        """(start, count) of the token rows this rank owns in mode 'rows'."""
+        return partition(M, self.world, self.rank)
+
+    def forward(self, x):
+        if self.mode == "rows" or self.world == 1:
+            return self.local_linear(x, self.weights)
+        M = x.shape[0]
+        n_local = self.N // self.world
+        out = torch.empty((M, self.N), dtype=torch.float16, device=x.device)
+        use_streams = x.is_cuda
+        comm_stream = torch.cuda.Stream() if use_streams else None
+        pending = []
+        for c in range(self.chunks):
+            r0, rows = partition(M, self.chunks, c)
+            if rows == 0:
+                continue
+            y = self.local_linear(x[r0:r0 + rows], self.weights)          # (rows, n_local)
+            # concatenated along dim 0 by the collective; viewed as (rank, row, column) afterwards
+            flat = torch.empty((self.world * rows, n_local), dtype=torch.float16, device=x.device)
+            gathered = flat.view(self.world, rows, n_local)
+            if use_streams:
+                ev = torch.cuda.Event()
+                ev.record()
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(ev)
+                    dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group)
+                    # interleave: out[r0+i, w*n_local + j] = gathered[w, i, j]
+                    out[r0:r0 + rows].view(rows, self.world, n_local).copy_(gathered.permute(1, 0, 2))
+                    done = torch.cuda.Event()
+                    done.record()
+                y.record_stream(comm_stream)
+                pending.append(done)
+            else:
+                dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group)
+                out[r0:r0 + rows].view(rows, self.world, n_local).copy_(gathered.permute(1, 0, 2))
+        for ev in pending:
+            torch.cuda.current_stream().wait_event(ev)
+        return out
+
+    __call__ = forward
