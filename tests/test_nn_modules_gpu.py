@@ -1,0 +1,99 @@
+"""The drop-in modules (forge_b200.nn / forge_b200.quant) on a GPU: conversion of a small
+nn.Module, state_dict round trip with the reference's buffer names and dtypes, agreement with
+the C-ABI calls they wrap (bit-exact) and with the fp16 model (loosely: it is a quantised model)."""
+import io
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+import oracle_lib as O
+from forge_b200 import _forge_C as C
+from forge_b200.nn import QuantizedLinear, SparseLinear, quantize_weight_per_channel
+from forge_b200.quant import quantize
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+class TinyMLP(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.up = nn.Linear(256, 512)
+        self.act = nn.SiLU()
+        self.down = nn.Linear(512, 256, bias=False)
+
+    def forward(self, x):
+        return self.down(self.act(self.up(x)))
+
+
+def test_quantized_linear_matches_cabi_and_oracle():
+    torch.manual_seed(0)
+    lin = nn.Linear(384, 272).to(DEV).half()
+    q = QuantizedLinear(384, 272).to(DEV)
+    q.quantize_weight(lin.weight.data)
+    q.bias.data.copy_(lin.bias.data)
+    x = torch.randn(5, 7, 384, device=DEV, dtype=torch.float16)      # extra leading dimension
+    y = q(x)
+    assert y.shape == (5, 7, 272)
+    x2 = x.reshape(-1, 384)
+    xq, xs = C.fused_quantize_activation(x2, 35, 384)
+    want = O.dequantize_bias(O.gemm_s32(xq.cpu().numpy(), q.w_int8.cpu().numpy()), xs.cpu().numpy(),
+                             q.w_scale.detach().cpu().numpy(), q.bias.detach().cpu().numpy(), gemm_epilogue=True)
+    assert np.array_equal(y.reshape(-1, 272).detach().cpu().numpy().view(np.uint16), want.view(np.uint16))
+    # close to the fp16 layer it replaces
+    ref = lin(x)
+    assert (y - ref).abs().max() < 0.05 * ref.abs().max() + 0.05
+    # weight recipe: absmax/127, round half even, clamp +-127
+    wq, ws = quantize_weight_per_channel(lin.weight.data)
+    assert torch.equal(wq, q.w_int8) and int(wq.abs().max()) == 127
+
+
+def test_backward_of_quantized_linear_runs():
+    q = QuantizedLinear(128, 64).to(DEV)
+    q.quantize_weight(torch.randn(64, 128))
+    x = torch.randn(16, 128, device=DEV, dtype=torch.float16, requires_grad=True)
+    q(x).float().sum().backward()
+    assert x.grad is not None and x.grad.shape == x.shape and q.bias.grad.shape == (64,)
+
+
+def test_sparse_linear_and_state_dict_round_trip():
+    torch.manual_seed(1)
+    w = torch.randn(208, 192)
+    s = SparseLinear(192, 208).to(DEV)
+    s.from_dense_weight(w)
+    sd = s.state_dict()
+    assert set(sd) == {"W_comp", "w_meta", "w_scale", "bias"}
+    assert sd["W_comp"].dtype == torch.int8 and sd["W_comp"].shape == (208, 96)
+    assert sd["w_meta"].dtype == torch.int32 and sd["w_meta"].shape == (208, 6)
+    assert sd["w_scale"].dtype == torch.float16
+    # compressed form equals the oracle's prune/compress/pack of the quantised weight
+    wq, _ = quantize_weight_per_channel(w)
+    comp, raw = O.prune_compress_24(wq.numpy())
+    assert np.array_equal(sd["W_comp"].cpu().numpy(), comp)
+    assert np.array_equal(sd["w_meta"].cpu().numpy().view(np.uint32), O.pack_metadata(raw, 208, 192))
+    buf = io.BytesIO()
+    torch.save(sd, buf)
+    buf.seek(0)
+    s2 = SparseLinear(192, 208).to(DEV)
+    s2.load_state_dict(torch.load(buf))
+    x = torch.randn(37, 192, device=DEV, dtype=torch.float16)
+    assert torch.equal(s(x), s2(x))
+    qd = QuantizedLinear(192, 208).state_dict()
+    assert set(qd) == {"w_int8", "w_scale", "bias"} and qd["w_int8"].dtype == torch.int8
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_quantize_converts_a_model(sparse):
+    torch.manual_seed(2)
+    model = TinyMLP().to(DEV).half()
+    qmodel = quantize(model, sparse=sparse, verbose=False)
+    kinds = {type(m).__name__ for m in qmodel.modules()}
+    assert "Linear" not in kinds and (("SparseLinear" in kinds) == sparse)
+    assert isinstance(model.up, nn.Linear), "the input model must be left untouched"
+    x = torch.randn(64, 256, device=DEV, dtype=torch.float16)
+    y, ref = qmodel(x), model(x)
+    assert y.shape == ref.shape and torch.isfinite(y).all()
+    if not sparse:
+        assert (y - ref).abs().max() < 0.1 * ref.abs().max() + 0.05
