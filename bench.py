@@ -453,7 +453,7 @@ def run_sharded_case(args):
     del W, raw
     w = SparseWeights(comp, meta, (torch.rand(n, generator=g, device=dev) * 0.01 + 0.001).half(), None)
     mode = "rows" if args.case == "shard_rows" else "columns"
-    layer = ShardedSparseLinear(w, mode, chunks=8)
+    layer = ShardedSparseLinear(w, mode, chunks=8, exchange=args.exchange)
     if mode == "rows":
         r0, rows = layer.rows_of(m)
         g.manual_seed(1000 + rank)
@@ -484,7 +484,7 @@ def run_sharded_case(args):
         line = {"case": args.case, "n_gpus": world, "shape": {"M": m, "K": k, "N": n}, "ms": ms,
                 "tokens_per_s": m / (ms * 1e-3), "dense_equiv_tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
                 "includes": "per-token quantize + 2:4-sparse GEMM + dequant" + (" + FP16 all-gather" if mode == "columns" else ""),
-                "steps": args.steps}
+                "steps": args.steps, "exchange": layer.exchange if mode == "columns" else None}
         if mode == "columns" and world > 1:
             recv = (world - 1) / world * 2.0 * m * n
             line["allgather_bytes_received_per_gpu"] = recv
@@ -506,6 +506,8 @@ def main():
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
+                    help="shard_cols: all-gather by the GEMM epilogue's peer stores (fused) or by NCCL")
     ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")
     args = ap.parse_args()
     if args.case in ("shard_rows", "shard_cols"):

@@ -32,6 +32,7 @@ SIGNATURES = {
     "forge_sparse_int8_linear": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i],
     "forge_splitk_reduce": [_vp, _vp, _vp, _i, _i, _vp],
     "forge_sparse_int8_gemm_s32": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "forge_sparse_int8_gemm_multi": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_longlong, _i, _i, _i, _vp],
     "forge_int8_gated_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "forge_sparse_int8_gated_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "forge_w8a8_gated_mlp_workspace_bytes": [_i, _i, _i],

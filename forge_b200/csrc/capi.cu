@@ -165,6 +165,13 @@ int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const
     return sparse_gemm_s32(W_comp, x_int8, w_meta, output, M, K, N_out, S(stream), g_force_sparse_bt);
 }
 
+int forge_sparse_int8_gemm_multi(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta,
+                                 const float* act_scale, const void* w_scale, const void* bias, void* const* outputs,
+                                 int n_outs, long long ld_out, int M, int K, int N_out, forge_stream_t stream) {
+    return sparse_gemm_dequant_multi(W_comp, x_int8, w_meta, act_scale, H(w_scale), H(bias), outputs, n_outs, ld_out,
+                                     M, K, N_out, S(stream));
+}
+
 int forge_int8_gated_gemm(const int8_t* x_int8, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
                           const void* wg_scale, const void* wu_scale, const void* bg, const void* bu, void* h_out,
                           int M, int K, int N, forge_stream_t stream) {

@@ -365,7 +365,7 @@ template <int BT, int EPI>
 __global__ void __launch_bounds__(kSpThreads, 1)
 sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
-                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out,
+                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
                    const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
@@ -584,7 +584,10 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     float as_lane = 0.f;
                     if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
                     tmem_ld_wait();
-                    store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                    if (EPI == 1 && multi.count > 0)
+                        store_transposed_chunk_multi(v, multi, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                    else
+                        store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -687,7 +690,8 @@ template <int BT, int EPI>
 int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
                        const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
                        cudaStream_t stream, const int8_t* W_comp2 = nullptr, const uint32_t* w_meta2 = nullptr,
-                       const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
+                       const __half* w_scale2 = nullptr, const __half* bias2 = nullptr,
+                       const OutDst* multi = nullptr) {
     using Cfg = SparsePairCfg<BT, EPI>;
     constexpr int CTA_W = (EPI == 2) ? 64 : 128;
     static int max_pairs[64] = {};
@@ -723,8 +727,11 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((N_out + 2 * CTA_W - 1) / (2 * CTA_W)) * ((M + BT - 1) / BT);
+    OutDst md = {};
+    if (multi != nullptr) md = *multi;
     return launch_pairs(sparse_pair_kernel<BT, EPI>, kSpThreads, Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
-                        tm_meta, tm_w2, tm_meta2, out, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, status);
+                        tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
+                        status);
 }
 
 template <int EPI>
@@ -759,6 +766,13 @@ int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int bt) {
     return sparse_pair_dispatch<1>(bt, W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+}
+
+int sparse_pair_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                              const __half* w_scale, const __half* bias, const OutDst* multi, int M, int K, int N_out,
+                              cudaStream_t stream) {
+    return launch_sparse_pair<224, 1>(W_comp, x, w_meta, act_scale, w_scale, bias, nullptr, M, K, N_out, stream,
+                                      nullptr, nullptr, nullptr, nullptr, multi);
 }
 
 int sparse_pair_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,

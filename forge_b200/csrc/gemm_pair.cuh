@@ -19,6 +19,12 @@ int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int bt);
 
+struct OutDst;
+// FP16 result written to every destination in `multi` (see sparse_epilogue.cuh).
+int sparse_pair_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                              const __half* w_scale, const __half* bias, const OutDst* multi, int M, int K, int N_out,
+                              cudaStream_t stream);
+
 // Gated (SiLU(gate) * up) sparse GEMM on CTA pairs; arguments as sparse_gemm_gated.
 int sparse_pair_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,
                       const int8_t* x, const float* act_scale, const __half* wg_scale, const __half* wu_scale,

@@ -88,7 +88,7 @@ template <int BT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
-                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out,
+                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
                    const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
@@ -317,7 +317,10 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     float as_lane = 0.f;
                     if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
                     tmem_ld_wait();
-                    store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                    if (EPI == 1 && multi.count > 0)
+                        store_transposed_chunk_multi(v, multi, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
+                    else
+                        store_transposed_chunk<EPI>(v, out, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -370,7 +373,7 @@ template <int BT, int EPI>
 int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
                   const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out,
                   cudaStream_t stream, const int8_t* W_comp2 = nullptr, const uint32_t* w_meta2 = nullptr,
-                  const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
+                  const __half* w_scale2 = nullptr, const __half* bias2 = nullptr, const OutDst* multi = nullptr) {
     using Cfg = SparseCfg<BT, EPI>;
     constexpr int TILE_W = (EPI == 2) ? BW / 2 : BW;
     static bool attr_set[64] = {};
@@ -417,8 +420,10 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((N_out + TILE_W - 1) / TILE_W) * ((M + BT - 1) / BT);
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_w2, tm_meta2, out, act_scale, w_scale,
-                                                      bias, w_scale2, bias2, M, N_out, K, status);
+    OutDst md = {};
+    if (multi != nullptr) md = *multi;
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_w2, tm_meta2, out, md, act_scale,
+                                                      w_scale, bias, w_scale2, bias2, M, N_out, K, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -481,6 +486,34 @@ int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int force_bt) {
     return sparse_dispatch<1>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream, force_bt);
+}
+
+int sparse_gemm_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                              const __half* w_scale, const __half* bias, void* const* outs, int n_outs,
+                              long long ld_out, int M, int K, int N_out, cudaStream_t stream) {
+    if (M <= 0 || K <= 0 || N_out <= 0 || n_outs <= 0) return kOk;
+    if (W_comp == nullptr || x == nullptr || w_meta == nullptr || act_scale == nullptr || w_scale == nullptr ||
+        outs == nullptr)
+        return kBadPointer;
+    if (n_outs > 8 || ld_out < N_out) return kBadShape;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    if (K % 128 != 0 || !aligned16(W_comp) || !aligned16(x) || !aligned16(w_meta)) return kBadShape;
+    OutDst md = {};
+    md.count = n_outs;
+    md.ld = ld_out;
+    for (int d = 0; d < n_outs; d++) {
+        if (outs[d] == nullptr) return kBadPointer;
+        md.ptr[d] = outs[d];
+    }
+    if (M >= 1024 && N_out >= 512) {
+        const int r = sparse_pair_dequant_multi(W_comp, x, w_meta, act_scale, w_scale, bias, &md, M, K, N_out, stream);
+        if (r >= 0) return r;
+    }
+    if (M > 64)
+        return launch_sparse<128, 1>(W_comp, x, w_meta, act_scale, w_scale, bias, nullptr, M, K, N_out, stream, nullptr,
+                                     nullptr, nullptr, nullptr, &md);
+    return launch_sparse<32, 1>(W_comp, x, w_meta, act_scale, w_scale, bias, nullptr, M, K, N_out, stream, nullptr,
+                                nullptr, nullptr, nullptr, &md);
 }
 
 int sparse_gemm_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,

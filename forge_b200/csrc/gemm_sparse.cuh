@@ -16,6 +16,14 @@ int sparse_gemm_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int force_bt);
 
+// FP16 result (M,N_out) written into each of `n_outs` (<= 8) buffers with row pitch `ld_out`
+// elements. The buffers may be peer-mapped memory of other GPUs: a column-sharded layer passes
+// every rank's copy of the full output, offset to its own first column, and the epilogue's
+// stores perform the all-gather. Needs K % 128 == 0 and 16-byte aligned operands.
+int sparse_gemm_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                              const __half* w_scale, const __half* bias, void* const* outs, int n_outs,
+                              long long ld_out, int M, int K, int N_out, cudaStream_t stream);
+
 // out (M,N_out) fp16 = fp16(SiLU(g) * u): gate and up projections (both 2:4 sparse, N_out rows
 // each) of a gated MLP in one pass. Needs K % 128 == 0 and 16-byte aligned operands (kBadShape).
 int sparse_gemm_gated(const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp, const uint32_t* wu_meta,

@@ -54,6 +54,39 @@ __device__ __forceinline__ void store_transposed_chunk(const uint32_t (&v)[32], 
 }
 
 
+// Destinations of the FP16 result: up to 8 buffers with a common row pitch. With one entry
+// this is the ordinary output; with several, entry d is typically GPU d's copy of the full
+// (M, N) output, peer-mapped over NVLink, and `ptr[d]` already points at this rank's first
+// column - the epilogue then performs the all-gather of a column-sharded layer as plain
+// peer stores, tile by tile, while the tensor cores work on the next tile.
+struct OutDst {
+    void* ptr[8];
+    long long ld;   // row pitch in elements
+    int count;
+};
+
+// As store_transposed_chunk<1>, to every destination.
+__device__ __forceinline__ void store_transposed_chunk_multi(const uint32_t (&v)[32], const OutDst& dst, int N_out,
+                                                             int M, int n, int m_first, float as_lane, float ws,
+                                                             float bs, bool has_bias) {
+    const int valid = min(32, M - m_first);
+    const bool col_ok = n < N_out;
+    __half h[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float as = __shfl_sync(0xffffffffu, as_lane, j);
+        h[j] = __float2half_rn(dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias));
+    }
+    if (!col_ok) return;
+    for (int d = 0; d < dst.count; d++) {
+        __half* p = static_cast<__half*>(dst.ptr[d]) + (size_t)m_first * dst.ld + n;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            if (j < valid) p[(size_t)j * dst.ld] = h[j];
+        }
+    }
+}
+
 // Gated (SiLU(gate) * up) epilogue of the sparse kernels. A 128-row weight tile holds 64 gate
 // rows (TMEM lanes 0-63) followed by the 64 up rows of the same output columns (lanes 64-127), so
 // gate and up of one output sit in two different warps. The up warp dequantises its 32 tokens in

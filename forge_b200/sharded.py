@@ -9,10 +9,15 @@ fp32 epilogue:
   rows     token rows are split across ranks, weights replicated. No communication at all: each
            rank quantizes and multiplies its own rows. This is the mode that scales linearly.
   columns  output channels (weight rows) are split across ranks, activations replicated; each
-           rank computes out[:, n0:n1] and the FP16 slices are all-gathered over NVLink. The
-           gather moves (g-1)/g * 2*M*N bytes into every GPU, so it is link-bound, not
-           compute-bound; rows are processed in chunks so the gather of chunk i overlaps the
-           GEMM of chunk i+1, and the column interleave is a copy out of the gather buffer.
+           rank computes out[:, n0:n1] and every rank ends up with the full (M, N) output. The
+           exchange moves (g-1)/g * 2*M*N bytes into every GPU, so it is link-bound, not
+           compute-bound. Two implementations:
+             fused  (default on GPUs) every rank's output buffer is mapped into every process
+                    (symmetric memory, else CUDA IPC) and the GEMM epilogue stores each tile
+                    straight into all g buffers - the all-gather is done by the kernel's own
+                    peer stores, tile by tile, overlapped with the tensor-core work.
+             nccl   rows are processed in chunks; the slice of chunk i is all-gathered with NCCL
+                    while the GEMM of chunk i+1 runs, then interleaved into place by a copy.
 
 The local compute is the C ABI of libforge_b200 (no fallback). `local_linear` can be injected so
 that the partition / gather / interleave logic is testable with gloo on CPUs.
@@ -55,6 +60,32 @@ def _forge_sparse_linear(x, w):
     return C.sparse_int8_linear(x, w.W_comp, w.w_meta, w.w_scale, w.bias, scratch_q, scratch_s)
 
 
+def map_peer_buffers(tensor, group=None):
+    """Maps `tensor` (same shape on every rank, one per GPU) into every process of `group`.
+    Returns (pointers, keepalive): pointers[r] is rank r's buffer as seen from this process.
+    Tries torch's symmetric memory first, then CUDA IPC through torch's storage sharing."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        buf = symm_mem.empty(tensor.shape, dtype=tensor.dtype, device=tensor.device)
+        hdl = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        return [int(p) for p in hdl.buffer_ptrs], (buf, hdl), buf
+    except Exception:
+        pass
+    info = tensor.untyped_storage()._share_cuda_()
+    infos = [None] * world
+    dist.all_gather_object(infos, info, group=group)
+    keep, ptrs = [], []
+    for r in range(world):
+        if r == rank:
+            ptrs.append(tensor.data_ptr())
+            continue
+        st = torch.UntypedStorage._new_shared_cuda(*infos[r])
+        keep.append(st)
+        ptrs.append(st.data_ptr() + tensor.storage_offset() * tensor.element_size())
+    return ptrs, keep, tensor
+
+
 class ShardedSparseLinear:
     """2:4-sparse W8A8 linear layer sharded over the ranks of `group`.
 
@@ -65,7 +96,7 @@ class ShardedSparseLinear:
                     (M, N) output on every rank.
     """
 
-    def __init__(self, weights, mode, group=None, chunks=4, local_linear=None):
+    def __init__(self, weights, mode, group=None, chunks=4, local_linear=None, exchange="auto"):
         if mode not in ("rows", "columns"):
             raise ValueError("mode must be 'rows' or 'columns'")
         self.mode = mode
@@ -74,6 +105,11 @@ class ShardedSparseLinear:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.chunks = max(1, chunks)
         self.local_linear = local_linear or _forge_sparse_linear
+        # "fused": all-gather by the GEMM epilogue's peer stores; "nccl": chunked NCCL all-gather
+        self.exchange = exchange
+        if exchange == "auto":
+            self.exchange = "fused" if (local_linear is None and weights.W_comp.is_cuda) else "nccl"
+        self._peer = None   # (M, pointers, keepalive, out tensor, sync scalar)
         self.N = weights.W_comp.shape[0]
         if mode == "columns":
             if self.N % self.world != 0:
@@ -92,6 +128,8 @@ class ShardedSparseLinear:
             return self.local_linear(x, self.weights)
         M = x.shape[0]
         n_local = self.N // self.world
+        if self.exchange == "fused":
+            return self._forward_fused(x)
         out = torch.empty((M, self.N), dtype=torch.float16, device=x.device)
         use_streams = x.is_cuda
         comm_stream = torch.cuda.Stream() if use_streams else None
@@ -121,6 +159,31 @@ class ShardedSparseLinear:
                 out[r0:r0 + rows].view(rows, self.world, n_local).copy_(gathered.permute(1, 0, 2))
         for ev in pending:
             torch.cuda.current_stream().wait_event(ev)
+        return out
+
+    def _forward_fused(self, x):
+        """Quantize locally, then one GEMM launch whose epilogue writes this rank's columns into
+        every rank's output buffer. Stream-ordered all-reduces of one scalar fence the exchange:
+        nobody overwrites a buffer a peer may still read, nobody reads before all have written."""
+        import ctypes
+        from . import _forge_C as C
+        from . import _lib
+        M, K = x.shape
+        n_local = self.N // self.world
+        if self._peer is None or self._peer[0] != M:
+            out = torch.empty((M, self.N), dtype=torch.float16, device=x.device)
+            ptrs, keep, out = map_peer_buffers(out, self.group)
+            self._peer = (M, ptrs, keep, out, torch.zeros(1, device=x.device))
+        _, ptrs, _, out, token = self._peer
+        xq, xs = C.fused_quantize_activation(x, M, K)
+        col0_bytes = self.rank * n_local * 2
+        arr = (ctypes.c_void_p * self.world)(*[p + col0_bytes for p in ptrs])
+        dist.all_reduce(token, group=self.group)          # every rank is done with the previous contents
+        w = self.weights
+        _lib.call("forge_sparse_int8_gemm_multi", w.W_comp.data_ptr(), xq.data_ptr(), w.w_meta.data_ptr(),
+                  xs.data_ptr(), w.w_scale.data_ptr(), 0 if w.bias is None else w.bias.data_ptr(), arr, self.world,
+                  self.N, M, K, n_local, torch.cuda.current_stream().cuda_stream)
+        dist.all_reduce(token, group=self.group)          # every rank's stores have landed
         return out
 
     __call__ = forward

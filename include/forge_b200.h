@@ -142,6 +142,18 @@ int forge_splitk_reduce(const float* workspace, const void* bias, void* output, 
 int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta, int32_t* output,
                                int M, int K, int N_out, forge_stream_t stream);
 
+/* Additive, no counterpart in the reference (which is single-GPU): forge_sparse_int8_gemm whose
+ * FP16 result (M,N_out) is written into each of n_outs (1..8) buffers with row pitch ld_out
+ * (elements, >= N_out). The buffers may be other GPUs' memory mapped into this process (CUDA
+ * IPC / peer access): a layer sharded by output channels passes every rank's copy of the full
+ * output, offset to its own first column, and the GEMM epilogue's stores carry out the
+ * all-gather over NVLink while later tiles are still being computed. The caller orders the
+ * ranks (nobody may read an output before every rank's kernel has finished). Needs K % 128 == 0
+ * and 16-byte aligned operands (FORGE_B200_BAD_SHAPE otherwise). */
+int forge_sparse_int8_gemm_multi(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta,
+                                 const float* act_scale, const void* w_scale, const void* bias, void* const* outputs,
+                                 int n_outs, long long ld_out, int M, int K, int N_out, forge_stream_t stream);
+
 /* ---------------------------------------------------------------- gated MLP (additive) */
 
 /* No counterpart in the reference (its only "gating" is an FP32 training op, src/nn/gating.cu).

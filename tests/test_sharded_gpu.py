@@ -44,10 +44,13 @@ def _worker(rank, world, port, results):
         rows = ShardedSparseLinear(w, "rows")
         r0, n = rows.rows_of(M)
         ok_rows = torch.equal(rows(x[r0:r0 + n]).view(torch.int16), full[r0:r0 + n].view(torch.int16))
-        cols = ShardedSparseLinear(w, "columns", chunks=3)
-        y = cols(x)
-        torch.cuda.synchronize()
-        ok_cols = torch.equal(y.view(torch.int16), full.view(torch.int16))
+        ok_cols = True
+        for exchange in ("nccl", "fused"):
+            cols = ShardedSparseLinear(w, "columns", chunks=3, exchange=exchange)
+            for _ in range(2):   # twice: the fused path reuses its peer-mapped output buffer
+                y = cols(x)
+                torch.cuda.synchronize()
+                ok_cols = ok_cols and torch.equal(y.view(torch.int16), full.view(torch.int16))
         results[rank] = (bool(ok_rows), bool(ok_cols), C.device_status())
     finally:
         dist.destroy_process_group()
