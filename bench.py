@@ -295,6 +295,8 @@ def run_case(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     lib = _lib.load()
+    lib.forge_b200_set_dense_tile(args.tile)
+    lib.forge_b200_set_sparse_tile(args.tile)
     peaks = _peaks()
     g = torch.Generator(device=dev)
     g.manual_seed(7)
@@ -421,7 +423,7 @@ def run_case(args):
     print(json.dumps({"case": name, "shape": shape, **extra, "ms": ms, "ms_min": min(times), "achieved": achieved,
                       "unit": unit,
                       "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
-                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps}))
+                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile}))
 
 
 def run_sharded_case(args):
@@ -506,6 +508,9 @@ def main():
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--tile", type=int, default=0,
+                    help="--case runs: pin the kernel tile (dense 64/128/256, 512 = CTA pair; sparse 32/64/128, "
+                         "1000+BT = CTA pair with BT tokens); 0 = automatic")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
                     help="shard_cols: all-gather by the GEMM epilogue's peer stores (fused) or by NCCL")
     ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")

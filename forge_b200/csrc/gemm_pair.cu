@@ -32,8 +32,11 @@ namespace {
 constexpr int kThreads = 192;
 constexpr int kEpiWarps = 4;
 constexpr int kEpiThreads = 128;
-constexpr int kSpEpiWarps = 8;            // sparse kernel: two warps per TMEM lane quarter
-constexpr int kSpThreads = 64 + 32 * kSpEpiWarps;
+// sparse kernel: epilogue warps per CTA - two per TMEM lane quarter, four for the gated epilogue
+// (measured: the heavier SiLU epilogue gains from 16 warps, the plain one loses a little)
+__host__ __device__ constexpr int sp_epi_warps(int epi) { return epi == 2 ? 16 : 8; }
+__host__ __device__ constexpr int sp_threads(int epi) { return 64 + 32 * sp_epi_warps(epi); }
+constexpr int kSpEpiWarpsMax = 16;
 
 // Shared bookkeeping at the tail of dynamic shared memory.
 struct PairBars {
@@ -337,7 +340,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 // [128r, 128r+128) with their metadata, and token rows [r*BT/2, (r+1)*BT/2) of the tile; its
 // TMEM receives weight rows [128r, 128r+128) x BT token columns.
 
-constexpr int kXbufBytes = 4 * 32 * 32 * (int)sizeof(float);   // gated epilogue: 4 warp pairs x 4 KB
+constexpr int kXbufBytes = (kSpEpiWarpsMax / 2) * 32 * 32 * (int)sizeof(float);   // gated epilogue: 4 KB per warp pair
 
 template <int BT, int EPI = 0>
 struct SparsePairCfg {
@@ -362,7 +365,7 @@ struct SparsePairCfg {
 };
 
 template <int BT, int EPI>
-__global__ void __launch_bounds__(kSpThreads, 1)
+__global__ void __launch_bounds__(sp_threads(EPI), 1)
 sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
                    const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
@@ -396,6 +399,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
 
+    constexpr int kSpEpiWarps = sp_epi_warps(EPI);
     if (threadIdx.x == 0) init_bars(bars, Cfg::kStages, kSpEpiWarps);
     if (warp_id == 0 && lane == 0) {
         prefetch_tensormap(&tm_w);
@@ -515,7 +519,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         int local = 0;
         if (EPI == 2) {
             const bool is_gate = q < 2;
-            const int pair = (q & 1) + 2 * chunk0;
+            const int pair = (q & 1) + 2 * chunk0;   // 0 .. kSpEpiWarps/2 - 1
             float* xbuf = smem_xbuf + pair * 1024;
             const __half* my_scale = is_gate ? w_scale : w_scale2;
             const __half* my_bias = is_gate ? bias : bias2;
@@ -729,7 +733,7 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     const long long tiles = (long long)((N_out + 2 * CTA_W - 1) / (2 * CTA_W)) * ((M + BT - 1) / BT);
     OutDst md = {};
     if (multi != nullptr) md = *multi;
-    return launch_pairs(sparse_pair_kernel<BT, EPI>, kSpThreads, Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
+    return launch_pairs(sparse_pair_kernel<BT, EPI>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
                         tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
                         status);
 }

@@ -89,36 +89,39 @@ __device__ __forceinline__ void store_transposed_chunk_multi(const uint32_t (&v)
 
 // Gated (SiLU(gate) * up) epilogue of the sparse kernels. A 128-row weight tile holds 64 gate
 // rows (TMEM lanes 0-63) followed by the 64 up rows of the same output columns (lanes 64-127), so
-// gate and up of one output sit in two different warps. The up warp dequantises its 32 tokens in
-// fp32 and hands them over through `xbuf` (32 tokens x 32 lanes fp32, 4 KB); the gate warp
-// dequantises its own, combines, rounds once to fp16 and stores. Two 64-thread named barriers
-// bracket the hand-over; both warps always reach them (a warp whose wait failed passes
+// gate and up of one output sit in two different warps. Both warps dequantise their 32 tokens in
+// fp32, then swap halves through `xbuf` (2 x 16 tokens x 32 lanes fp32, 4 KB): the gate warp
+// receives u of tokens 0-15 and finishes those, the up warp receives g of tokens 16-31 and
+// finishes these - each combines, rounds once to fp16 and stores 16 tokens. Two 64-thread named
+// barriers bracket the swap; both warps always reach them (a warp whose wait failed passes
 // ok = false and only synchronises).
 __device__ __forceinline__ void gated_chunk(bool is_gate, bool ok, const uint32_t (&v)[32], float* xbuf, int bar_id,
                                             __half* __restrict__ out, int N_out, int M, int n, int m_first,
                                             float as_lane, float ws, float bs, bool has_bias) {
     const int lane = threadIdx.x & 31;
     float d[32];
+    float* give = xbuf + (is_gate ? 512 : 0);   // gate hands over g[16..31], up hands over u[0..15]
+    float* take = xbuf + (is_gate ? 0 : 512);
     if (ok) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
             const float as = __shfl_sync(0xffffffffu, as_lane, j);
             d[j] = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
         }
-        if (!is_gate) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) xbuf[j * 32 + lane] = d[j];
-        }
+        for (int j = 0; j < 16; j++) give[j * 32 + lane] = is_gate ? d[16 + j] : d[j];
     }
     asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-    if (is_gate && ok) {
+    if (ok) {
+        const int first = is_gate ? 0 : 16;          // the 16 tokens this warp finishes
         const int valid = min(32, M - m_first);
         const bool col_ok = n < N_out;
-        __half* p = out + (size_t)m_first * N_out + n;
+        __half* p = out + (size_t)(m_first + first) * N_out + n;
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const float h = silu_mul(d[j], xbuf[j * 32 + lane]);
-            if (j < valid && col_ok) p[(size_t)j * N_out] = __float2half_rn(h);
+        for (int j = 0; j < 16; j++) {
+            const float other = take[j * 32 + lane];
+            const float h = is_gate ? silu_mul(d[j], other) : silu_mul(other, d[16 + j]);
+            if (first + j < valid && col_ok) p[(size_t)j * N_out] = __float2half_rn(h);
         }
     }
     asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
