@@ -37,6 +37,11 @@ constexpr int kEpiThreads = 128;
 __host__ __device__ constexpr int sp_epi_warps(int epi) { return epi == 2 ? 16 : 8; }
 __host__ __device__ constexpr int sp_threads(int epi) { return 64 + 32 * sp_epi_warps(epi); }
 constexpr int kSpEpiWarpsMax = 16;
+// weight-row blocks per raster band of the sparse kernel: the activations are re-read from DRAM
+// once per band, the band's weights stay in L2
+constexpr int kSparseBand = 16;
+// row blocks (of 256) per raster band of the dense pair kernel
+constexpr int kDenseBand = 16;
 
 // Shared bookkeeping at the tail of dynamic shared memory.
 struct PairBars {
@@ -163,7 +168,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             uint32_t phase = 0;
             bool ok = true;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-                const TileCoord tc = tile_coord(t, m_blocks, n_blocks, 8);
+                const TileCoord tc = tile_coord(t, m_blocks, n_blocks, kDenseBand);
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
                         atomicExch(status, 301);
@@ -236,11 +241,12 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         uint8_t* my_stage = smem_epi + (warp_id - 2) * Cfg::kEpiBufs * Cfg::kEpiBufBytes;
         constexpr int CH = (EPI == 0) ? 32 : 64;
         const bool has_bias = (bias != nullptr);
+        const uint64_t store_policy = l2_policy_evict_first();   // outputs must not push operands out of L2
         int local = 0;
         int sbuf = 0;
         bool ok = true;
         for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
-            const TileCoord tc = tile_coord(t, m_blocks, n_blocks, 8);
+            const TileCoord tc = tile_coord(t, m_blocks, n_blocks, kDenseBand);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row0 = tc.a_blk * 256 + (int)rank * 128;
@@ -309,7 +315,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&tm_c, stg, n0 + c * CH, row0 + q * 32);
+                    tma_store_2d_hint(&tm_c, stg, n0 + c * CH, row0 + q * 32, store_policy);
                     tma_store_commit();
                 }
                 sbuf = (sbuf + 1) % Cfg::kEpiBufs;
@@ -424,7 +430,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
                 const int w_row = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W;
                 const int t_row = tc.b_blk * BT + (int)rank * HT;
                 for (int kb = 0; kb < num_kb; kb++) {
@@ -525,7 +531,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const __half* my_bias = is_gate ? bias : bias2;
             bool ok = true;   // after a failed wait: keep meeting the partner warp at the barriers
             for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
-                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
                 const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
                 const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
                 const int n = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W + (q & 1) * 32 + lane;
@@ -563,7 +569,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             }
         } else {
             for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
-                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, 4);
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
                 const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
                 const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
                 const int n = tc.a_blk * 256 + (int)rank * 128 + q * 32 + lane;

@@ -24,7 +24,7 @@ __device__ __forceinline__ void store_transposed_chunk(const uint32_t (&v)[32], 
         int32_t* p = static_cast<int32_t*>(out) + (size_t)m_first * N_out + n;
         if (full) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) p[(size_t)j * N_out] = static_cast<int32_t>(v[j]);
+            for (int j = 0; j < 32; j++) __stcs(p + (size_t)j * N_out, static_cast<int32_t>(v[j]));
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
@@ -38,7 +38,10 @@ __device__ __forceinline__ void store_transposed_chunk(const uint32_t (&v)[32], 
             for (int j = 0; j < 32; j++) {
                 const float as = __shfl_sync(0xffffffffu, as_lane, j);
                 const float o = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
-                p[(size_t)j * N_out] = __float2half_rn(o);
+                // streaming store: the output is not read again by this kernel and must not push
+                // the activations out of L2
+                __stcs(reinterpret_cast<unsigned short*>(p + (size_t)j * N_out),
+                       __half_as_ushort(__float2half_rn(o)));
             }
         } else {
 #pragma unroll
