@@ -301,7 +301,7 @@ def run_case(args):
     g = torch.Generator(device=dev)
     g.manual_seed(7)
     name = args.case
-    s = torch.cuda.current_stream().cuda_stream
+    S = [torch.cuda.current_stream().cuda_stream]   # the stream the calls go to (swapped for graph capture)
 
     def ri8(*shape):
         return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev)
@@ -324,22 +324,22 @@ def run_case(args):
             if name == "sparse":
                 fn = lambda: lib.forge_sparse_int8_gemm(comp.data_ptr(), x.data_ptr(), meta.data_ptr(), a_s.data_ptr(),
                                                         w_s.data_ptr(), bias.data_ptr(), out.data_ptr(), m, k, n, 0, 1,
-                                                        s, -1)
+                                                        S[0], -1)
             else:
                 fn = lambda: lib.forge_sparse_int8_gemm_s32(comp.data_ptr(), x.data_ptr(), meta.data_ptr(),
-                                                            out.data_ptr(), m, k, n, s)
+                                                            out.data_ptr(), m, k, n, S[0])
         elif name == "dense":
             fn = lambda: lib.forge_int8_gemm_dequant(x.data_ptr(), W.data_ptr(), a_s.data_ptr(), w_s.data_ptr(),
-                                                     bias.data_ptr(), out.data_ptr(), m, k, n, s)
+                                                     bias.data_ptr(), out.data_ptr(), m, k, n, S[0])
         else:
-            fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, s)
+            fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, S[0])
         shape = {"M": m, "N": n, "K": k}
     elif name == "quantize":
         m, k = args.m or 16384, args.k or 8192
         x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
         q = torch.empty((m, k), dtype=torch.int8, device=dev)
         sc = torch.empty((m,), dtype=torch.float32, device=dev)
-        fn = lambda: lib.forge_fused_quantize_activation(x.data_ptr(), q.data_ptr(), sc.data_ptr(), m, k, s)
+        fn = lambda: lib.forge_fused_quantize_activation(x.data_ptr(), q.data_ptr(), sc.data_ptr(), m, k, S[0])
         work, unit, bound, shape = (3.0 * m * k + 4.0 * m) / 1e9, "GB/s", "hbm", {"M": m, "K": k}
     elif name == "dequant":
         m, n = args.m or 8192, args.n or 8192
@@ -349,7 +349,7 @@ def run_case(args):
         bias = torch.rand(n, generator=g, device=dev).half()
         out = torch.empty((m, n), dtype=torch.float16, device=dev)
         fn = lambda: lib.forge_fused_dequantize_bias(acc.data_ptr(), a_s.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
-                                                     out.data_ptr(), m, n, s)
+                                                     out.data_ptr(), m, n, S[0])
         work, unit, bound, shape = (6.0 * m * n + 4.0 * m + 4.0 * n) / 1e9, "GB/s", "hbm", {"M": m, "N": n}
     elif name in ("prune", "pack"):
         n, k = args.n or 28672, args.k or 8192
@@ -359,10 +359,10 @@ def run_case(args):
         meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
         C.prune_compress_24(W, comp, raw, n, k)
         if name == "prune":
-            fn = lambda: lib.forge_prune_compress_24(W.data_ptr(), comp.data_ptr(), raw.data_ptr(), n, k, s)
+            fn = lambda: lib.forge_prune_compress_24(W.data_ptr(), comp.data_ptr(), raw.data_ptr(), n, k, S[0])
             work = 1.75 * n * k / 1e9
         else:
-            fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, s)
+            fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, S[0])
             work = 0.375 * n * k / 1e9
         unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
     elif name in ("mlp", "mlp_sparse"):
@@ -382,7 +382,7 @@ def run_case(args):
         if name == "mlp":
             fn = lambda: lib.forge_w8a8_gated_mlp(x.data_ptr(), Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(),
                                                   sg.data_ptr(), su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(),
-                                                  m, dm, df, ws.data_ptr(), s)
+                                                  m, dm, df, ws.data_ptr(), S[0])
         else:
             packs = []
             for W in (Wg, Wu, Wd):
@@ -395,7 +395,7 @@ def run_case(args):
                 packs += [comp, meta]
             fn = lambda: lib.forge_sparse_w8a8_gated_mlp(x.data_ptr(), *[t.data_ptr() for t in packs], sg.data_ptr(),
                                                          su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(), m, dm,
-                                                         df, ws.data_ptr(), s)
+                                                         df, ws.data_ptr(), S[0])
         work, unit, bound = 3 * 2.0 * m * dm * df / 1e12, "TOP/s", "tensor"
         shape = {"tokens": m, "d_model": dm, "d_ffn": df}
     else:
@@ -405,16 +405,36 @@ def run_case(args):
     for _ in range(args.warmup):
         assert fn() == 0
     torch.cuda.synchronize()
+    if args.graph:
+        # the reference's protocol (benchmarks/bench_int8_sparse.cu:41-85): `reps` calls captured in
+        # a CUDA graph, replays timed with events - device time without host launch latency
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            S[0] = side.cuda_stream
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(args.reps):
+                    assert fn() == 0
+        S[0] = torch.cuda.current_stream().cuda_stream
+        one_call = fn
+        fn = lambda: (graph.replay(), 0)[1]
+        reps_in_fn, args.reps = args.reps, 1
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+    else:
+        reps_in_fn = 1
     times = []
     for _ in range(args.steps):
         if flush is not None:
             flush.fill_(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        assert fn() == 0
+        for _ in range(args.reps):
+            assert fn() == 0
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
+        times.append(e0.elapsed_time(e1) / (args.reps * reps_in_fn))
     assert lib.forge_b200_device_status(1) == 0
     ms = statistics.median(times)
     achieved = work / (ms * 1e-3)
@@ -423,7 +443,7 @@ def run_case(args):
     print(json.dumps({"case": name, "shape": shape, **extra, "ms": ms, "ms_min": min(times), "achieved": achieved,
                       "unit": unit,
                       "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
-                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile}))
+                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile, "reps": args.reps * reps_in_fn, "cuda_graph": bool(args.graph)}))
 
 
 def run_sharded_case(args):
@@ -511,6 +531,10 @@ def main():
     ap.add_argument("--tile", type=int, default=0,
                     help="--case runs: pin the kernel tile (dense 64/128/256, 512 = CTA pair; sparse 32/64/128, "
                          "1000+BT = CTA pair with BT tokens); 0 = automatic")
+    ap.add_argument("--reps", type=int, default=1,
+                    help="--case runs: back-to-back calls per timed region (hides host launch latency of "
+                         "microsecond-sized kernels; inputs then stay in L2 after the first call)")
+    ap.add_argument("--graph", type=int, default=0, help="--case runs: capture --reps calls in a CUDA graph and time replays")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
                     help="shard_cols: all-gather by the GEMM epilogue's peer stores (fused) or by NCCL")
     ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 
 namespace fb200 {
 
@@ -151,8 +152,43 @@ inline PFN_encodeTiled get_encode_fn() {
 
 // Encodes a tiled tensor map of up to 3 dimensions. dims/box are in elements (innermost
 // first), strides_bytes[i] is the byte stride of dimension i+1. Returns false on failure.
+// Encoding costs about a microsecond of host time per map and a launch needs three to five of
+// them, which matters for microsecond-sized problems, so each host thread keeps the last maps it
+// built (keyed by every encode argument; a map depends on nothing else).
 inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+    struct Key {
+        const void* base;
+        uint64_t dims[3];
+        uint64_t strides[2];
+        uint32_t box[3];
+        int dtype, rank, swizzle;
+    };
+    struct Entry {
+        Key key;
+        CUtensorMap map;
+        bool valid;
+    };
+    constexpr int kSlots = 64;
+    thread_local Entry cache[kSlots] = {};
+    Key k = {};
+    k.base = base;
+    k.dtype = (int)dtype;
+    k.rank = rank;
+    k.swizzle = (int)swizzle;
+    for (int i = 0; i < rank; i++) {
+        k.dims[i] = dims[i];
+        k.box[i] = box[i];
+    }
+    for (int i = 0; i + 1 < rank; i++) k.strides[i] = strides_bytes[i];
+    uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.dims[0] * 31 + k.dims[1]) * 0xC2B2AE3D27D4EB4Full + k.box[0] * 131 + k.box[1] * 17 + k.box[2] +
+         (uint64_t)k.swizzle * 7 + (uint64_t)k.dtype * 3 + k.dims[2] * 1315423911ull;
+    Entry& e = cache[(h >> 32) % kSlots];
+    if (e.valid && memcmp(&e.key, &k, sizeof(Key)) == 0) {
+        *out = e.map;
+        return true;
+    }
     PFN_encodeTiled fn = get_encode_fn();
     if (fn == nullptr) return false;
     cuuint64_t gdim[3];
@@ -167,7 +203,11 @@ inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, con
     const CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    e.key = k;
+    e.map = *out;
+    e.valid = true;
+    return true;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

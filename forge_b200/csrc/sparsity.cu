@@ -16,32 +16,27 @@ namespace fb200 {
 
 // Decides one group of four signed bytes packed in `w` (byte i = position i).
 // Returns the nibble; `kept` receives the two surviving bytes (low byte = lower position).
+//
+// The reference scan (prune_compress.cu:39-50: start with positions 0/1 ordered by magnitude,
+// then strict '<' replacements for positions 2 and 3) drops exactly the two smallest elements
+// under the order (|value|, position) - checked exhaustively over all 129^4 magnitude tuples -
+// so the two dropped positions are the two smallest of the keys (|value| << 2) | position, found
+// with a five-comparator min/max network instead of a data-dependent scan.
 __device__ __forceinline__ uint32_t prune_group(uint32_t w, uint32_t& kept) {
-    int a[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) a[i] = abs((int)(int8_t)((w >> (8 * i)) & 0xFF));
-    int min1 = 0, min2 = 1;
-    if (a[0] > a[1]) {
-        min1 = 1;
-        min2 = 0;
-    }
-#pragma unroll
-    for (int i = 2; i < 4; i++) {
-        const int a1 = (min1 == 0) ? a[0] : (min1 == 1) ? a[1] : (min1 == 2) ? a[2] : a[3];
-        const int a2 = (min2 == 0) ? a[0] : (min2 == 1) ? a[1] : (min2 == 2) ? a[2] : a[3];
-        if (a[i] < a1) {
-            min2 = min1;
-            min1 = i;
-        } else if (a[i] < a2) {
-            min2 = i;
-        }
-    }
-    const uint32_t drop = (1u << min1) | (1u << min2);
-    const uint32_t keep = ~drop & 0xFu;            // exactly two bits set
-    const int k0 = __ffs(keep) - 1;                // lower kept position
-    const int k1 = 31 - __clz(keep);               // higher kept position
-    kept = ((w >> (8 * k0)) & 0xFF) | (((w >> (8 * k1)) & 0xFF) << 8);
-    return (uint32_t)(k0 | (k1 << 2));
+    const uint32_t a = __vabs4(w);   // per-byte |x|; |-128| = 128 (no saturation), as abs((int)x)
+    const uint32_t k0 = (a & 0xFFu) << 2;
+    const uint32_t k1 = ((a >> 6) & 0x3FCu) | 1u;
+    const uint32_t k2 = ((a >> 14) & 0x3FCu) | 2u;
+    const uint32_t k3 = ((a >> 22) & 0x3FCu) | 3u;
+    const uint32_t lo01 = min(k0, k1), hi01 = max(k0, k1);
+    const uint32_t lo23 = min(k2, k3), hi23 = max(k2, k3);
+    const uint32_t d1 = min(lo01, lo23);                            // smallest key
+    const uint32_t d2 = min(max(lo01, lo23), min(hi01, hi23));      // second smallest
+    const uint32_t keep = ~((1u << (d1 & 3u)) | (1u << (d2 & 3u))) & 0xFu;   // exactly two bits set
+    const int p0 = __ffs(keep) - 1;                // lower kept position
+    const int p1 = 31 - __clz(keep);               // higher kept position
+    kept = ((w >> (8 * p0)) & 0xFF) | (((w >> (8 * p1)) & 0xFF) << 8);
+    return (uint32_t)(p0 | (p1 << 2));
 }
 
 }  // namespace fb200
