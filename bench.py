@@ -32,9 +32,9 @@ OPS_PER_STEP = 2.0 * M * N * K
 METRIC = "int8_gemm_dequant_tops_m8192_n8192_k8192"
 UNIT = "TOPS"
 CPU_SAMPLE_ROWS = 256
-# dram__bytes_read.sum + dram__bytes_write.sum of one dense_gemm_kernel<256,1> launch at 8192^3
-# (profiles/dense_gemm_kernel_8192.md: 333.1 MB read + 114.4 MB written).
-NCU_DRAM_BYTES_PER_LAUNCH = 447.5e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one dense_pair_kernel<1> launch at 8192^3
+# (profiles/dense_pair_kernel_8192.md: 234.1 MB read + 117.5 MB written).
+NCU_DRAM_BYTES_PER_LAUNCH = 351.6e6
 
 
 def _peaks():
@@ -255,7 +255,7 @@ def run_b200(args):
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": 2.0 * peak_bf16, "unit": "TOP/s",
         "frac": achieved / (2.0 * peak_bf16), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-        "kernel": "dense_gemm_kernel<256,1> (tcgen05.mma kind::i8, 128x256 tiles)",
+        "kernel": "dense_pair_kernel<1> (tcgen05.mma cta_group::2 kind::i8, 256x256 tiles per SM pair)",
         "peak_basis": f"2 x {'sustained' if sustained else 'burst'} cuBLAS bf16 TFLOP/s of {peaks['source']} "
                       "(kind::i8 issues at twice the bf16 rate); nominal dense int8 is 4500",
         "frac_of_nominal_4500": achieved / 4500.0,
