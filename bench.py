@@ -365,6 +365,29 @@ def run_case(args):
             fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, S[0])
             work = 0.375 * n * k / 1e9
         unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
+    elif name in ("sparse_linear_fused", "sparse_linear_two_pass"):
+        # fp16 in -> quantize -> 2:4 GEMM -> fp16 out; the reference's showcase shape for its fused path
+        # (include/forge/gemm/int8_sparse.cuh:82) by default
+        m, k, n = args.m or 147456, args.k or 1280, args.n or 320
+        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
+        W = ri8(n, k)
+        comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+        raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+        meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+        C.prune_compress_24(W, comp, raw, n, k)
+        C.pack_metadata(raw, meta, n, k)
+        w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
+        bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
+        out = torch.empty((m, n), dtype=torch.float16, device=dev)
+        sq = torch.empty((m, k), dtype=torch.int8, device=dev)
+        ss = torch.empty((m,), dtype=torch.float32, device=dev)
+        path = 1 if name == "sparse_linear_fused" else 0
+        fn = lambda: lib.forge_sparse_int8_linear(x.data_ptr(), comp.data_ptr(), meta.data_ptr(), w_s.data_ptr(),
+                                                  bias.data_ptr(), out.data_ptr(), m, k, n, sq.data_ptr(),
+                                                  ss.data_ptr(), 0, 1, S[0], path)
+        # minimum traffic: read x (fp16) and the compressed weight once, write the fp16 output
+        work, unit, bound = (2.0 * m * k + 0.625 * n * k + 2.0 * m * n) / 1e9, "GB/s", "hbm"
+        shape = {"M": m, "K": k, "N": n}
     elif name in ("mlp", "mlp_sparse"):
         # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
         m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336

@@ -42,14 +42,14 @@ def int8_linear(x, w_int8, w_scale, bias, scratch_a_int8, scratch_a_scale):
 
 
 def sparse_int8_linear(x, W_comp, w_meta, w_scale, bias, scratch_x_int8, scratch_x_scale, splitk_workspace=None,
-                       split_k=1):
+                       split_k=1, path=-1):
     """bindings.cpp:521-554 -> float16 (M,N_out). The workspace is accepted for compatibility;
     this implementation never splits K, so none is allocated."""
     M, K, N_out = x.size(0), x.size(1), W_comp.size(0)
     output = torch.empty((M, N_out), dtype=x.dtype, device=x.device)
     _lib.call("forge_sparse_int8_linear", _ptr(x), _ptr(W_comp), _ptr(w_meta), _ptr(w_scale), _ptr(bias),
               _ptr(output), M, K, N_out, _ptr(scratch_x_int8), _ptr(scratch_x_scale), _ptr(splitk_workspace),
-              split_k, _stream(), -1)
+              split_k, _stream(), path)
     return output
 
 
@@ -94,6 +94,25 @@ def sparse_int8_gemm_s32(W_comp, x_int8, w_meta):
     _lib.call("forge_sparse_int8_gemm_s32", _ptr(W_comp), _ptr(x_int8), _ptr(w_meta), _ptr(output), M, K, N_out,
               _stream())
     return output
+
+
+def prepare_weight(weight, sparse):
+    """Float weight (N, K), fp32 or fp16, on a GPU -> (w_int8 or None, W_comp or None, w_meta or None,
+    w_scale fp16) in one kernel: per-channel quantisation and, with sparse=True, 2:4 prune +
+    compress + metadata pack."""
+    if weight.dtype not in (torch.float32, torch.float16):
+        weight = weight.to(torch.float32)
+    weight = weight.contiguous()
+    N, K = weight.shape
+    dev = weight.device
+    w_scale = torch.empty((N,), dtype=torch.float16, device=dev)
+    w_int8 = None if sparse else torch.empty((N, K), dtype=torch.int8, device=dev)
+    W_comp = torch.empty((N, K // 2), dtype=torch.int8, device=dev) if sparse else None
+    w_meta = torch.empty((N, K // 32), dtype=torch.int32, device=dev) if sparse else None
+    with torch.cuda.device(dev):
+        _lib.call("forge_prepare_weight", _ptr(weight), 1 if weight.dtype == torch.float16 else 0, _ptr(w_int8),
+                  _ptr(W_comp), _ptr(w_meta), _ptr(w_scale), N, K, _stream())
+    return w_int8, W_comp, w_meta, w_scale
 
 
 def device_status(reset=True):

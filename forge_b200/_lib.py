@@ -40,6 +40,7 @@ SIGNATURES = {
     "forge_sparse_w8a8_gated_mlp": [_vp] * 14 + [_i, _i, _i, _vp, _vp],
     "forge_prune_compress_24": [_vp, _vp, _vp, _i, _i, _vp],
     "forge_pack_metadata": [_vp, _vp, _i, _i, _vp],
+    "forge_prepare_weight": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "forge_b200_set_dense_tile": [_i],
     "forge_b200_set_sparse_tile": [_i],
     "forge_b200_device_status": [_i],

@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "gemm_dense.cuh"
 #include "gemm_sparse.cuh"
+#include "gemm_fq.cuh"
 #include "kernels.cuh"
 
 using namespace fb200;
@@ -130,6 +131,12 @@ int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uin
                                S(stream), bt);
 }
 
+// Policy of the automatic path (the reference's is sp_use_fused, src/gemm/int8_sparse.cu:930-938,
+// which fuses narrow layers whose activation does not fit L2 on an RTX 4090). On B200 the two-pass
+// path won every measured shape - at the reference's showcase shape (M = 147456, K = 1280,
+// N_out = 320) 0.18 ms against 0.36 ms for the fused kernel, whose quantize prologue cannot overlap
+// the MMAs on its single resident block - so the automatic path never fuses. The fused kernel
+// stays available through kSparseLinearFused (bit-identical output, no scratch buffers).
 int forge_sparse_int8_linear_fused(int M, int K, int N_out) {
     (void)M;
     (void)K;
@@ -141,8 +148,14 @@ int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t
                              const void* bias, void* output, int M, int K, int N_out, int8_t* scratch_x_int8,
                              float* scratch_x_scale, float* splitk_workspace, int split_k, forge_stream_t stream,
                              int path) {
-    (void)path;
     if (M <= 0 || K <= 0 || N_out <= 0) return kOk;
+    // Fused quantize + GEMM: forced, or chosen when the caller did not ask for a specific split-K
+    // (same rule as the reference, int8_sparse.cu:1026-1034). It does not touch the scratch buffers.
+    const bool can_fuse = sparse_fq_fits(K, x) && aligned16(W_comp) && aligned16(w_meta);
+    if (can_fuse && (path == FORGE_SPARSE_LINEAR_FUSED ||
+                     (path == FORGE_SPARSE_LINEAR_AUTO && split_k <= 1 &&
+                      forge_sparse_int8_linear_fused(M, K, N_out) != 0)))
+        return sparse_fq_linear(H(x), W_comp, w_meta, H(w_scale), H(bias), H(output), M, K, N_out, S(stream));
     if (scratch_x_int8 == nullptr || scratch_x_scale == nullptr) return kBadPointer;
     const int r = quantize_activation(H(x), scratch_x_int8, scratch_x_scale, M, K, S(stream));
     if (r != kOk) return r;
@@ -268,6 +281,11 @@ int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* m
 
 int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, forge_stream_t stream) {
     return pack_metadata(meta_raw, meta_packed, N, K, S(stream));
+}
+
+int forge_prepare_weight(const void* weight, int weight_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta,
+                         void* w_scale, int N, int K, forge_stream_t stream) {
+    return prepare_weight(weight, weight_is_half, w_int8, W_comp, w_meta, H(w_scale), N, K, S(stream));
 }
 
 void forge_b200_set_dense_tile(int bn) { g_force_dense_bn = bn; }

@@ -356,7 +356,8 @@ struct SparsePairCfg {
     static constexpr int kMetaBytes = 128 * 32;
     static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
     static constexpr int kBarBytes = 256;
-    static constexpr int kFixed = kBarBytes + (EPI == 2 ? kXbufBytes : 0);
+    // EPI 2: gate/up exchange buffers; EPI 1: two 8 KB transposition buffers of the multi-destination store
+    static constexpr int kFixed = kBarBytes + (EPI == 2 ? kXbufBytes : (EPI == 1 ? 16384 : 0));
     static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesMax > 6 ? 6 : kStagesMax;
     static constexpr int kSmemBytes = kStages * kStageBytes + kFixed;
@@ -386,8 +387,9 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* smem_stage = smem;
     float* smem_xbuf = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
-    const PairBars bars =
-        carve_bars(smem + Cfg::kStages * Cfg::kStageBytes + (EPI == 2 ? kXbufBytes : 0), Cfg::kStages);
+    uint8_t* smem_tr = smem + Cfg::kStages * Cfg::kStageBytes;   // EPI 1: transposition buffers
+    const PairBars bars = carve_bars(smem + Cfg::kStages * Cfg::kStageBytes + (Cfg::kFixed - Cfg::kBarBytes),
+                                     Cfg::kStages);
 
     const int warp_id = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -560,6 +562,48 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     }
                     gated_chunk(is_gate, ok, v, xbuf, 4 + pair, static_cast<__half*>(out), N_out, M, n, m_first,
                                 as_lane, ws, bs, my_bias != nullptr);
+                }
+                if (ok) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                }
+            }
+        } else if (EPI == 1 && multi.count > 0 && multi.vec != 0) {
+            // several destinations (peer GPUs): wide row-segment stores through a transposition buffer
+            uint8_t* stage = smem_tr + chunk0 * 8192;
+            bool ok = true;   // after a failed wait: keep meeting the group at the barriers
+            for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n_base = tc.a_blk * 256 + (int)rank * 128;
+                const int n = n_base + q * 32 + lane;
+                const int m0 = tc.b_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (n < N_out) {
+                    ws = __half2float(w_scale[n]);
+                    if (has_bias) bs = __half2float(bias[n]);
+                }
+                if (ok) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag));
+                    if (!ok) atomicExch(status, 404);
+                }
+                if (ok) tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+                for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M) break;
+                    uint32_t v[32];
+                    float as_lane = 0.f;
+                    if (ok) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                        if (m_first + lane < M) as_lane = act_scale[m_first + lane];
+                        tmem_ld_wait();
+                    }
+                    store_chunk_multi_vec(ok, v, multi, stage, 8 + chunk0, q, N_out, M, n_base, m_first, as_lane, ws,
+                                          bs, has_bias);
                 }
                 if (ok) {
                     tc_fence_before();

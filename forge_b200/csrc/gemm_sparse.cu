@@ -501,9 +501,11 @@ int sparse_gemm_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint3
     OutDst md = {};
     md.count = n_outs;
     md.ld = ld_out;
+    md.vec = (ld_out % 8 == 0 && N_out % 8 == 0) ? 1 : 0;
     for (int d = 0; d < n_outs; d++) {
         if (outs[d] == nullptr) return kBadPointer;
         md.ptr[d] = outs[d];
+        if (!aligned16(outs[d])) md.vec = 0;
     }
     if (M >= 1024 && N_out >= 512) {
         const int r = sparse_pair_dequant_multi(W_comp, x, w_meta, act_scale, w_scale, bias, &md, M, K, N_out, stream);

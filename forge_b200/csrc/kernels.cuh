@@ -13,6 +13,10 @@ int dequantize_bias(const int32_t* input, const float* act_scale, const __half* 
 int prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
                       cudaStream_t stream);
 int pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, cudaStream_t stream);
+// fp32 / fp16 weight (N,K) -> per-channel int8 (optional), 2:4 compressed values + packed metadata
+// (optional) and fp16 scales, in one pass. Needs K % 32 == 0.
+int prepare_weight(const void* w, int w_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta, __half* w_scale,
+                   int N, int K, cudaStream_t stream);
 
 }  // namespace fb200
 

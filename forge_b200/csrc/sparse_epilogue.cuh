@@ -66,6 +66,7 @@ struct OutDst {
     void* ptr[8];
     long long ld;   // row pitch in elements
     int count;
+    int vec;        // 1: every ptr is 16-byte aligned and ld % 8 == 0 -> 16-byte row-segment stores
 };
 
 // As store_transposed_chunk<1>, to every destination.
@@ -88,6 +89,48 @@ __device__ __forceinline__ void store_transposed_chunk_multi(const uint32_t (&v)
             if (j < valid) p[(size_t)j * dst.ld] = h[j];
         }
     }
+}
+
+// Multi-destination store with wide segments, for the four warps that together hold one
+// 32-token x 128-column chunk (one warp per TMEM lane quarter). The chunk is transposed through
+// `stage` (32 rows x 256 bytes) so that a half-warp then owns one whole 256-byte output row
+// segment and writes it to every destination with 16-byte stores: peer writes over NVLink travel
+// as 256-byte contiguous runs instead of 64-byte ones. Two 128-thread named barriers bracket
+// the transpose; all four warps always reach them (ok = false: synchronise only).
+__device__ __forceinline__ void store_chunk_multi_vec(bool ok, const uint32_t (&v)[32], const OutDst& dst,
+                                                      uint8_t* stage, int bar_id, int q, int N_out, int M,
+                                                      int n_base, int m_first, float as_lane, float ws, float bs,
+                                                      bool has_bias) {
+    const int lane = threadIdx.x & 31;
+    if (ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float as = __shfl_sync(0xffffffffu, as_lane, j);
+            const float o = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
+            *reinterpret_cast<__half*>(stage + j * 256 + (q * 32 + lane) * 2) = __float2half_rn(o);
+        }
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    if (ok) {
+        const int valid = min(32, M - m_first);
+        const int col = n_base + (lane & 15) * 8;          // first of this lane's 8 columns
+        const bool col_ok = col + 8 <= N_out;              // N_out % 8 == 0 on this path
+        uint4 seg[4];
+        int rows[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            rows[i] = q * 8 + 2 * i + (lane >> 4);
+            seg[i] = *reinterpret_cast<const uint4*>(stage + rows[i] * 256 + (lane & 15) * 16);
+        }
+        for (int d = 0; d < dst.count; d++) {
+            __half* base = static_cast<__half*>(dst.ptr[d]) + (size_t)m_first * dst.ld + col;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (rows[i] < valid && col_ok) *reinterpret_cast<uint4*>(base + (size_t)rows[i] * dst.ld) = seg[i];
+            }
+        }
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 }
 
 // Gated (SiLU(gate) * up) epilogue of the sparse kernels. A 128-row weight tile holds 64 gate

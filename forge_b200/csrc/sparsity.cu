@@ -130,6 +130,67 @@ pack_metadata_vec_kernel(const uint4* __restrict__ meta_raw, uint2* __restrict__
     meta_packed[id] = make_uint2(out[0], out[1]);
 }
 
+// One pass from a floating-point weight to everything a W8A8 layer stores: per-output-channel
+// symmetric quantisation (scale = absmax / 127 floored at 1e-8, round half to even, clamp +-127,
+// scale kept as fp16 - the recipe of the reference's Python modules,
+// python/forge/nn/linear.py:167-173,234-249, with IEEE divides so the values equal torch's), then
+// 2:4 prune + compress + metadata pack of the int8 row. One block per weight row; a thread turns
+// 32 consecutive weights (8 groups) into 16 compressed bytes and one packed metadata word.
+__device__ __forceinline__ float load_w(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load_w(const __half* p) { return __half2float(__ldg(p)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+prepare_weight_kernel(const T* __restrict__ w, int8_t* __restrict__ w_int8, int8_t* __restrict__ W_comp,
+                      uint32_t* __restrict__ w_meta, __half* __restrict__ w_scale, int K) {
+    const int row = blockIdx.x;
+    const T* wr = w + (size_t)row * K;
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(load_w(wr + k)));
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = part[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, part[i]);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    if (threadIdx.x == 0) w_scale[row] = __float2half_rn(scale);
+    for (int c = threadIdx.x; c < K / 32; c += blockDim.x) {     // c: run of 32 weights
+        uint32_t q[8];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float v = rintf(__fdiv_rn(load_w(wr + c * 32 + g * 4 + i), scale));
+                const int qi = (int)fminf(fmaxf(v, -127.f), 127.f);
+                word |= ((uint32_t)qi & 0xFFu) << (8 * i);
+            }
+            q[g] = word;
+        }
+        if (w_int8 != nullptr) {
+            uint4* d = reinterpret_cast<uint4*>(w_int8 + (size_t)row * K + c * 32);
+            d[0] = make_uint4(q[0], q[1], q[2], q[3]);
+            d[1] = make_uint4(q[4], q[5], q[6], q[7]);
+        }
+        if (W_comp != nullptr) {
+            uint32_t comp[4] = {0u, 0u, 0u, 0u};
+            uint32_t meta = 0;
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+                uint32_t kept;
+                const uint32_t nib = prune_group(q[g], kept);
+                comp[g >> 1] |= kept << (16 * (g & 1));
+                meta |= nib << (4 * g);
+            }
+            *reinterpret_cast<uint4*>(W_comp + (size_t)row * (K / 2) + c * 16) =
+                make_uint4(comp[0], comp[1], comp[2], comp[3]);
+            w_meta[(size_t)row * (K / 32) + c] = meta;
+        }
+    }
+}
+
 }  // namespace
 
 int prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
@@ -169,6 +230,22 @@ int pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, 
         forge::sparsity::pack_metadata_kernel<<<(unsigned)((words + 255) / 256), 256, 0, stream>>>(meta_raw,
                                                                                                   meta_packed, N, K);
     }
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+int prepare_weight(const void* w, int w_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta, __half* w_scale,
+                   int N, int K, cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return kOk;
+    if (w == nullptr || w_scale == nullptr || (w_int8 == nullptr && W_comp == nullptr)) return kBadPointer;
+    if (W_comp != nullptr && w_meta == nullptr) return kBadPointer;
+    if (K % 32 != 0 || (w_int8 != nullptr && !aligned16(w_int8)) || (W_comp != nullptr && !aligned16(W_comp)))
+        return kBadShape;
+    if (w_is_half)
+        prepare_weight_kernel<__half><<<N, 256, 0, stream>>>(static_cast<const __half*>(w), w_int8, W_comp, w_meta,
+                                                            w_scale, K);
+    else
+        prepare_weight_kernel<float><<<N, 256, 0, stream>>>(static_cast<const float*>(w), w_int8, W_comp, w_meta,
+                                                           w_scale, K);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 

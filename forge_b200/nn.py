@@ -83,7 +83,10 @@ class QuantizedLinear(nn.Module, _ScratchMixin):
 
     @torch.no_grad()
     def quantize_weight(self, weight_fp):
-        q, scale = quantize_weight_per_channel(weight_fp)
+        if self.w_int8.is_cuda:   # one kernel on the module's device (IEEE arithmetic, = torch on the CPU)
+            q, _, _, scale = _C.prepare_weight(weight_fp.detach().to(self.w_int8.device), sparse=False)
+        else:
+            q, scale = quantize_weight_per_channel(weight_fp)
         self.w_int8.copy_(q)
         self.w_scale.data.copy_(scale)
 
@@ -120,12 +123,10 @@ class SparseLinear(nn.Module, _ScratchMixin):
         dev = self.W_comp.device
         if dev.type != "cuda":
             raise RuntimeError("move the module to a CUDA device before from_dense_weight()")
-        q, scale = quantize_weight_per_channel(weight_fp.to(dev))
-        N, K = q.shape
-        raw = torch.empty(N * K // 4, dtype=torch.uint8, device=dev)
-        with torch.cuda.device(dev):
-            _C.prune_compress_24(q.contiguous(), self.W_comp, raw, N, K)
-            _C.pack_metadata(raw, self.w_meta, N, K)
+        # one kernel: per-channel quantisation + 2:4 prune + compress + metadata pack
+        _, comp, meta, scale = _C.prepare_weight(weight_fp.detach().to(dev), sparse=True)
+        self.W_comp.copy_(comp)
+        self.w_meta.copy_(meta)
         self.w_scale.data.copy_(scale)
 
     def extra_repr(self):

@@ -201,6 +201,15 @@ int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* m
  * src/sparsity/pack_metadata.cu:32-44. meta_raw (N*K/4) -> meta_packed (N,K/32) uint32. */
 int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, forge_stream_t stream);
 
+/* Additive: weight preparation in one kernel. The reference does it with PyTorch ops followed by
+ * prune_compress_24 + pack_metadata and a synchronize (python/forge/nn/linear.py:167-173,234-249).
+ * weight (N,K) fp32 (weight_is_half = 0) or fp16 (1) -> per output channel scale = absmax/127
+ * (floored at 1e-8), q = clamp(round_half_even(w / scale), +-127): w_int8 (N,K) (may be NULL),
+ * w_scale (N) fp16, and - when W_comp is not NULL - the 2:4 pruned + compressed weight (N,K/2)
+ * with its packed metadata (N,K/32). Needs K % 32 == 0 and 16-byte aligned outputs. */
+int forge_prepare_weight(const void* weight, int weight_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta,
+                         void* w_scale, int N, int K, forge_stream_t stream);
+
 /* ---------------------------------------------------------------- diagnostics (additive) */
 
 /* Tuning/testing knobs: pin the dense tile width (64/128/256) or the sparse token-tile width

@@ -46,8 +46,8 @@ def test_quantized_linear_matches_cabi_and_oracle():
     ref = lin(x)
     assert (y - ref).abs().max() < 0.05 * ref.abs().max() + 0.05
     # weight recipe: absmax/127, round half even, clamp +-127
-    wq, ws = quantize_weight_per_channel(lin.weight.data)
-    assert torch.equal(wq, q.w_int8) and int(wq.abs().max()) == 127
+    wq, ws = quantize_weight_per_channel(lin.weight.data.cpu())
+    assert torch.equal(wq.to(DEV), q.w_int8) and int(wq.abs().max()) == 127
 
 
 def test_backward_of_quantized_linear_runs():
@@ -69,7 +69,7 @@ def test_sparse_linear_and_state_dict_round_trip():
     assert sd["w_meta"].dtype == torch.int32 and sd["w_meta"].shape == (208, 6)
     assert sd["w_scale"].dtype == torch.float16
     # compressed form equals the oracle's prune/compress/pack of the quantised weight
-    wq, _ = quantize_weight_per_channel(w)
+    wq, _ = quantize_weight_per_channel(w)        # on the CPU: IEEE arithmetic
     comp, raw = O.prune_compress_24(wq.numpy())
     assert np.array_equal(sd["W_comp"].cpu().numpy(), comp)
     assert np.array_equal(sd["w_meta"].cpu().numpy().view(np.uint32), O.pack_metadata(raw, 208, 192))
@@ -82,6 +82,28 @@ def test_sparse_linear_and_state_dict_round_trip():
     assert torch.equal(s(x), s2(x))
     qd = QuantizedLinear(192, 208).state_dict()
     assert set(qd) == {"w_int8", "w_scale", "bias"} and qd["w_int8"].dtype == torch.int8
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("N,K", [(208, 192), (33, 64), (1000, 4096)])
+def test_one_pass_weight_preparation_equals_the_torch_recipe(dtype, N, K):
+    """forge_prepare_weight against the reference's recipe (torch per-channel quantisation, then
+    prune_compress_24 + pack_metadata), bit for bit."""
+    g = torch.Generator().manual_seed(N + K)
+    w = (torch.randn((N, K), generator=g) * 0.02).to(dtype)
+    w[0] = 0                      # an all-zero channel exercises the 1e-8 floor
+    w[1, :8] = w[1, 8]            # ties inside groups
+    # the recipe with IEEE arithmetic = torch on the CPU (torch's CUDA kernels replace the division
+    # by the scalar 127 with a multiplication by its reciprocal, which moves some scales by one ulp)
+    wq, ws = quantize_weight_per_channel(w)
+    wq, ws = wq.to(DEV), ws.to(DEV)
+    q_dense, _, _, s_dense = C.prepare_weight(w.to(DEV), sparse=False)
+    assert torch.equal(q_dense, wq) and torch.equal(s_dense.view(torch.int16), ws.view(torch.int16))
+    _, comp, meta, s_sparse = C.prepare_weight(w.to(DEV), sparse=True)
+    comp_cpu, raw_cpu = O.prune_compress_24(wq.cpu().numpy())
+    assert np.array_equal(comp.cpu().numpy(), comp_cpu)
+    assert np.array_equal(meta.cpu().numpy().view(np.uint32), O.pack_metadata(raw_cpu, N, K))
+    assert torch.equal(s_sparse.view(torch.int16), ws.view(torch.int16))
 
 
 @pytest.mark.parametrize("sparse", [False, True])
