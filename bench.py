@@ -306,127 +306,136 @@ def run_case(args):
     def ri8(*shape):
         return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev)
 
-    work, unit, bound = None, None, None
-    if name in ("dense", "dense_s32", "sparse", "sparse_s32"):
-        m, n, k = args.m or 8192, args.n or 8192, args.k or 8192
-        a_s = torch.rand(m, generator=g, device=dev) * 0.05 + 0.001
-        w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
-        bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
-        x, W = ri8(m, k), ri8(n, k)
-        out = torch.empty((m, n), dtype=torch.int32 if name.endswith("s32") else torch.float16, device=dev)
-        work, unit, bound = 2.0 * m * n * k / 1e12, "TOP/s", "tensor"
-        if name.startswith("sparse"):
+    def build_case():
+        # one complete operand set + the call on it; --rotate builds several so that back-to-back
+        # calls inside a CUDA graph each read operands that are not in L2
+        work, unit, bound = None, None, None
+        if name in ("dense", "dense_s32", "sparse", "sparse_s32"):
+            m, n, k = args.m or 8192, args.n or 8192, args.k or 8192
+            a_s = torch.rand(m, generator=g, device=dev) * 0.05 + 0.001
+            w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
+            bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
+            x, W = ri8(m, k), ri8(n, k)
+            out = torch.empty((m, n), dtype=torch.int32 if name.endswith("s32") else torch.float16, device=dev)
+            work, unit, bound = 2.0 * m * n * k / 1e12, "TOP/s", "tensor"
+            if name.startswith("sparse"):
+                comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+                raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+                meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+                C.prune_compress_24(W, comp, raw, n, k)
+                C.pack_metadata(raw, meta, n, k)
+                if name == "sparse":
+                    fn = lambda: lib.forge_sparse_int8_gemm(comp.data_ptr(), x.data_ptr(), meta.data_ptr(), a_s.data_ptr(),
+                                                            w_s.data_ptr(), bias.data_ptr(), out.data_ptr(), m, k, n, 0, 1,
+                                                            S[0], -1)
+                else:
+                    fn = lambda: lib.forge_sparse_int8_gemm_s32(comp.data_ptr(), x.data_ptr(), meta.data_ptr(),
+                                                                out.data_ptr(), m, k, n, S[0])
+            elif name == "dense":
+                fn = lambda: lib.forge_int8_gemm_dequant(x.data_ptr(), W.data_ptr(), a_s.data_ptr(), w_s.data_ptr(),
+                                                         bias.data_ptr(), out.data_ptr(), m, k, n, S[0])
+            else:
+                fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, S[0])
+            shape = {"M": m, "N": n, "K": k}
+        elif name == "quantize":
+            m, k = args.m or 16384, args.k or 8192
+            x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
+            q = torch.empty((m, k), dtype=torch.int8, device=dev)
+            sc = torch.empty((m,), dtype=torch.float32, device=dev)
+            fn = lambda: lib.forge_fused_quantize_activation(x.data_ptr(), q.data_ptr(), sc.data_ptr(), m, k, S[0])
+            work, unit, bound, shape = (3.0 * m * k + 4.0 * m) / 1e9, "GB/s", "hbm", {"M": m, "K": k}
+        elif name == "dequant":
+            m, n = args.m or 8192, args.n or 8192
+            acc = torch.randint(-50000, 50000, (m, n), generator=g, dtype=torch.int32, device=dev)
+            a_s = torch.rand(m, generator=g, device=dev)
+            w_s = torch.rand(n, generator=g, device=dev).half()
+            bias = torch.rand(n, generator=g, device=dev).half()
+            out = torch.empty((m, n), dtype=torch.float16, device=dev)
+            fn = lambda: lib.forge_fused_dequantize_bias(acc.data_ptr(), a_s.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
+                                                         out.data_ptr(), m, n, S[0])
+            work, unit, bound, shape = (6.0 * m * n + 4.0 * m + 4.0 * n) / 1e9, "GB/s", "hbm", {"M": m, "N": n}
+        elif name in ("prune", "pack"):
+            n, k = args.n or 28672, args.k or 8192
+            W = ri8(n, k)
+            comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
+            raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
+            meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
+            C.prune_compress_24(W, comp, raw, n, k)
+            if name == "prune":
+                fn = lambda: lib.forge_prune_compress_24(W.data_ptr(), comp.data_ptr(), raw.data_ptr(), n, k, S[0])
+                work = 1.75 * n * k / 1e9
+            else:
+                fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, S[0])
+                work = 0.375 * n * k / 1e9
+            unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
+        elif name in ("sparse_linear_fused", "sparse_linear_two_pass"):
+            # fp16 in -> quantize -> 2:4 GEMM -> fp16 out; the reference's showcase shape for its fused path
+            # (include/forge/gemm/int8_sparse.cuh:82) by default
+            m, k, n = args.m or 147456, args.k or 1280, args.n or 320
+            x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
+            W = ri8(n, k)
             comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
             raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
             meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
             C.prune_compress_24(W, comp, raw, n, k)
             C.pack_metadata(raw, meta, n, k)
-            if name == "sparse":
-                fn = lambda: lib.forge_sparse_int8_gemm(comp.data_ptr(), x.data_ptr(), meta.data_ptr(), a_s.data_ptr(),
-                                                        w_s.data_ptr(), bias.data_ptr(), out.data_ptr(), m, k, n, 0, 1,
-                                                        S[0], -1)
+            w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
+            bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
+            out = torch.empty((m, n), dtype=torch.float16, device=dev)
+            sq = torch.empty((m, k), dtype=torch.int8, device=dev)
+            ss = torch.empty((m,), dtype=torch.float32, device=dev)
+            path = 1 if name == "sparse_linear_fused" else 0
+            fn = lambda: lib.forge_sparse_int8_linear(x.data_ptr(), comp.data_ptr(), meta.data_ptr(), w_s.data_ptr(),
+                                                      bias.data_ptr(), out.data_ptr(), m, k, n, sq.data_ptr(),
+                                                      ss.data_ptr(), 0, 1, S[0], path)
+            # minimum traffic: read x (fp16) and the compressed weight once, write the fp16 output
+            work, unit, bound = (2.0 * m * k + 0.625 * n * k + 2.0 * m * n) / 1e9, "GB/s", "hbm"
+            shape = {"M": m, "K": k, "N": n}
+        elif name in ("mlp", "mlp_sparse"):
+            # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
+            m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
+            x = torch.randn((m, dm), generator=g, device=dev, dtype=torch.float16)
+
+            def qweight(rows, cols):
+                w = torch.randn((rows, cols), generator=g, device=dev) * 0.02
+                sc = w.abs().amax(dim=1).clamp(min=1e-8) / 127.0
+                wq = torch.clamp(torch.round(w / sc[:, None]), -127, 127).to(torch.int8)
+                return wq, sc.to(torch.float16)
+
+            (Wg, sg), (Wu, su), (Wd, sd) = qweight(df, dm), qweight(df, dm), qweight(dm, df)
+            outp = torch.empty((m, dm), dtype=torch.float16, device=dev)
+            ws = torch.empty(lib.forge_w8a8_gated_mlp_workspace_bytes(m, dm, df), dtype=torch.uint8, device=dev)
+            if name == "mlp":
+                fn = lambda: lib.forge_w8a8_gated_mlp(x.data_ptr(), Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(),
+                                                      sg.data_ptr(), su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(),
+                                                      m, dm, df, ws.data_ptr(), S[0])
             else:
-                fn = lambda: lib.forge_sparse_int8_gemm_s32(comp.data_ptr(), x.data_ptr(), meta.data_ptr(),
-                                                            out.data_ptr(), m, k, n, S[0])
-        elif name == "dense":
-            fn = lambda: lib.forge_int8_gemm_dequant(x.data_ptr(), W.data_ptr(), a_s.data_ptr(), w_s.data_ptr(),
-                                                     bias.data_ptr(), out.data_ptr(), m, k, n, S[0])
+                packs = []
+                for W in (Wg, Wu, Wd):
+                    n_, k_ = W.shape
+                    comp = torch.empty((n_, k_ // 2), dtype=torch.int8, device=dev)
+                    raw = torch.empty((n_ * (k_ // 4),), dtype=torch.uint8, device=dev)
+                    meta = torch.empty((n_, k_ // 32), dtype=torch.int32, device=dev)
+                    C.prune_compress_24(W, comp, raw, n_, k_)
+                    C.pack_metadata(raw, meta, n_, k_)
+                    packs += [comp, meta]
+                fn = lambda: lib.forge_sparse_w8a8_gated_mlp(x.data_ptr(), *[t.data_ptr() for t in packs], sg.data_ptr(),
+                                                             su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(), m, dm,
+                                                             df, ws.data_ptr(), S[0])
+            work, unit, bound = 3 * 2.0 * m * dm * df / 1e12, "TOP/s", "tensor"
+            shape = {"tokens": m, "d_model": dm, "d_ffn": df}
         else:
-            fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, S[0])
-        shape = {"M": m, "N": n, "K": k}
-    elif name == "quantize":
-        m, k = args.m or 16384, args.k or 8192
-        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
-        q = torch.empty((m, k), dtype=torch.int8, device=dev)
-        sc = torch.empty((m,), dtype=torch.float32, device=dev)
-        fn = lambda: lib.forge_fused_quantize_activation(x.data_ptr(), q.data_ptr(), sc.data_ptr(), m, k, S[0])
-        work, unit, bound, shape = (3.0 * m * k + 4.0 * m) / 1e9, "GB/s", "hbm", {"M": m, "K": k}
-    elif name == "dequant":
-        m, n = args.m or 8192, args.n or 8192
-        acc = torch.randint(-50000, 50000, (m, n), generator=g, dtype=torch.int32, device=dev)
-        a_s = torch.rand(m, generator=g, device=dev)
-        w_s = torch.rand(n, generator=g, device=dev).half()
-        bias = torch.rand(n, generator=g, device=dev).half()
-        out = torch.empty((m, n), dtype=torch.float16, device=dev)
-        fn = lambda: lib.forge_fused_dequantize_bias(acc.data_ptr(), a_s.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
-                                                     out.data_ptr(), m, n, S[0])
-        work, unit, bound, shape = (6.0 * m * n + 4.0 * m + 4.0 * n) / 1e9, "GB/s", "hbm", {"M": m, "N": n}
-    elif name in ("prune", "pack"):
-        n, k = args.n or 28672, args.k or 8192
-        W = ri8(n, k)
-        comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
-        raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
-        meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
-        C.prune_compress_24(W, comp, raw, n, k)
-        if name == "prune":
-            fn = lambda: lib.forge_prune_compress_24(W.data_ptr(), comp.data_ptr(), raw.data_ptr(), n, k, S[0])
-            work = 1.75 * n * k / 1e9
-        else:
-            fn = lambda: lib.forge_pack_metadata(raw.data_ptr(), meta.data_ptr(), n, k, S[0])
-            work = 0.375 * n * k / 1e9
-        unit, bound, shape = "GB/s", "hbm", {"N": n, "K": k}
-    elif name in ("sparse_linear_fused", "sparse_linear_two_pass"):
-        # fp16 in -> quantize -> 2:4 GEMM -> fp16 out; the reference's showcase shape for its fused path
-        # (include/forge/gemm/int8_sparse.cuh:82) by default
-        m, k, n = args.m or 147456, args.k or 1280, args.n or 320
-        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
-        W = ri8(n, k)
-        comp = torch.empty((n, k // 2), dtype=torch.int8, device=dev)
-        raw = torch.empty((n * (k // 4),), dtype=torch.uint8, device=dev)
-        meta = torch.empty((n, k // 32), dtype=torch.int32, device=dev)
-        C.prune_compress_24(W, comp, raw, n, k)
-        C.pack_metadata(raw, meta, n, k)
-        w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
-        bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
-        out = torch.empty((m, n), dtype=torch.float16, device=dev)
-        sq = torch.empty((m, k), dtype=torch.int8, device=dev)
-        ss = torch.empty((m,), dtype=torch.float32, device=dev)
-        path = 1 if name == "sparse_linear_fused" else 0
-        fn = lambda: lib.forge_sparse_int8_linear(x.data_ptr(), comp.data_ptr(), meta.data_ptr(), w_s.data_ptr(),
-                                                  bias.data_ptr(), out.data_ptr(), m, k, n, sq.data_ptr(),
-                                                  ss.data_ptr(), 0, 1, S[0], path)
-        # minimum traffic: read x (fp16) and the compressed weight once, write the fp16 output
-        work, unit, bound = (2.0 * m * k + 0.625 * n * k + 2.0 * m * n) / 1e9, "GB/s", "hbm"
-        shape = {"M": m, "K": k, "N": n}
-    elif name in ("mlp", "mlp_sparse"):
-        # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
-        m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
-        x = torch.randn((m, dm), generator=g, device=dev, dtype=torch.float16)
+            raise SystemExit(f"unknown case {name}")
+        return fn, work, unit, bound, shape
 
-        def qweight(rows, cols):
-            w = torch.randn((rows, cols), generator=g, device=dev) * 0.02
-            sc = w.abs().amax(dim=1).clamp(min=1e-8) / 127.0
-            wq = torch.clamp(torch.round(w / sc[:, None]), -127, 127).to(torch.int8)
-            return wq, sc.to(torch.float16)
-
-        (Wg, sg), (Wu, su), (Wd, sd) = qweight(df, dm), qweight(df, dm), qweight(dm, df)
-        outp = torch.empty((m, dm), dtype=torch.float16, device=dev)
-        ws = torch.empty(lib.forge_w8a8_gated_mlp_workspace_bytes(m, dm, df), dtype=torch.uint8, device=dev)
-        if name == "mlp":
-            fn = lambda: lib.forge_w8a8_gated_mlp(x.data_ptr(), Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(),
-                                                  sg.data_ptr(), su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(),
-                                                  m, dm, df, ws.data_ptr(), S[0])
-        else:
-            packs = []
-            for W in (Wg, Wu, Wd):
-                n_, k_ = W.shape
-                comp = torch.empty((n_, k_ // 2), dtype=torch.int8, device=dev)
-                raw = torch.empty((n_ * (k_ // 4),), dtype=torch.uint8, device=dev)
-                meta = torch.empty((n_, k_ // 32), dtype=torch.int32, device=dev)
-                C.prune_compress_24(W, comp, raw, n_, k_)
-                C.pack_metadata(raw, meta, n_, k_)
-                packs += [comp, meta]
-            fn = lambda: lib.forge_sparse_w8a8_gated_mlp(x.data_ptr(), *[t.data_ptr() for t in packs], sg.data_ptr(),
-                                                         su.data_ptr(), sd.data_ptr(), 0, 0, 0, outp.data_ptr(), m, dm,
-                                                         df, ws.data_ptr(), S[0])
-        work, unit, bound = 3 * 2.0 * m * dm * df / 1e12, "TOP/s", "tensor"
-        shape = {"tokens": m, "d_model": dm, "d_ffn": df}
-    else:
-        raise SystemExit(f"unknown case {name}")
+    sets = [build_case() for _ in range(max(1, args.rotate))]
+    fn, work, unit, bound, shape = sets[0]
+    fns = [s[0] for s in sets]
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.flush_l2 else None
     for _ in range(args.warmup):
-        assert fn() == 0
+        for f in fns:
+            assert f() == 0
     torch.cuda.synchronize()
     if args.graph:
         # the reference's protocol (benchmarks/bench_int8_sparse.cu:41-85): `reps` calls captured in
@@ -436,10 +445,9 @@ def run_case(args):
         with torch.cuda.stream(side):
             S[0] = side.cuda_stream
             with torch.cuda.graph(graph, stream=side):
-                for _ in range(args.reps):
-                    assert fn() == 0
+                for r in range(args.reps):
+                    assert fns[r % len(fns)]() == 0
         S[0] = torch.cuda.current_stream().cuda_stream
-        one_call = fn
         fn = lambda: (graph.replay(), 0)[1]
         reps_in_fn, args.reps = args.reps, 1
         for _ in range(3):
@@ -466,7 +474,8 @@ def run_case(args):
     print(json.dumps({"case": name, "shape": shape, **extra, "ms": ms, "ms_min": min(times), "achieved": achieved,
                       "unit": unit,
                       "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
-                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile, "reps": args.reps * reps_in_fn, "cuda_graph": bool(args.graph)}))
+                      "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile, "reps": args.reps * reps_in_fn, "cuda_graph": bool(args.graph),
+                      "rotating_operand_sets": len(fns)}))
 
 
 def run_sharded_case(args):
@@ -557,6 +566,9 @@ def main():
     ap.add_argument("--reps", type=int, default=1,
                     help="--case runs: back-to-back calls per timed region (hides host launch latency of "
                          "microsecond-sized kernels; inputs then stay in L2 after the first call)")
+    ap.add_argument("--rotate", type=int, default=1,
+                    help="--case runs with --graph: number of separate operand sets the captured calls cycle through "
+                         "(sets x bytes per set above the L2 size makes every call read from HBM)")
     ap.add_argument("--graph", type=int, default=0, help="--case runs: capture --reps calls in a CUDA graph and time replays")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
                     help="shard_cols: all-gather by the GEMM epilogue's peer stores (fused) or by NCCL")

@@ -115,6 +115,34 @@ def prepare_weight(weight, sparse):
     return w_int8, W_comp, w_meta, w_scale
 
 
+def int8_conv2d_forward(input, weight, w_scale, bias, kernel_size, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+    """INT8 conv2d (forge::nn::int8_conv2d_forward; the reference has no Python binding for it): input
+    (N,C_in,H,W) fp16, weight (C_out, C_in*kH*kW) int8, w_scale / bias (C_out) fp16 -> (N,C_out,H_out,W_out)
+    fp16, each output position's patch quantized per row."""
+    N, C_in, H, W = input.shape
+    C_out = weight.shape[0]
+    (kH, kW), (pH, pW), (sH, sW), (dH, dW) = kernel_size, padding, stride, dilation
+    Ho = (H + 2 * pH - dH * (kH - 1) - 1) // sH + 1
+    Wo = (W + 2 * pW - dW * (kW - 1) - 1) // sW + 1
+    out = torch.empty((N, C_out, Ho, Wo), dtype=torch.float16, device=input.device)
+    with torch.cuda.device(input.device):
+        _lib.call("forge_int8_conv2d_forward", _ptr(input), _ptr(weight), _ptr(w_scale), _ptr(bias), _ptr(out), N, C_in,
+                  H, W, C_out, kH, kW, pH, pW, sH, sW, dH, dW, None, _stream())
+    return out
+
+
+def int8_conv_transpose2d_k2s2_forward(input, weight, w_scale, bias):
+    """2x2 stride-2 INT8 transposed conv (forge::nn::int8_conv_transpose2d_k2s2_forward): weight
+    (4*C_out, C_in) int8 with row co*4 + kh*2 + kw -> (N,C_out,2H,2W) fp16."""
+    N, C_in, H, W = input.shape
+    C_out = weight.shape[0] // 4
+    out = torch.empty((N, C_out, 2 * H, 2 * W), dtype=torch.float16, device=input.device)
+    with torch.cuda.device(input.device):
+        _lib.call("forge_int8_conv_transpose2d_k2s2_forward", _ptr(input), _ptr(weight), _ptr(w_scale), _ptr(bias),
+                  _ptr(out), N, C_in, H, W, C_out, None, _stream())
+    return out
+
+
 def device_status(reset=True):
     """Status word of the current device: 0 unless a kernel gave up on a bounded wait."""
     return _lib.load().forge_b200_device_status(1 if reset else 0)

@@ -41,6 +41,10 @@ SIGNATURES = {
     "forge_prune_compress_24": [_vp, _vp, _vp, _i, _i, _vp],
     "forge_pack_metadata": [_vp, _vp, _i, _i, _vp],
     "forge_prepare_weight": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "forge_int8_conv2d_workspace_size": [_i] * 12,
+    "forge_int8_conv2d_forward": [_vp] * 5 + [_i] * 13 + [_vp, _vp],
+    "forge_int8_conv_transpose2d_k2s2_workspace_size": [_i] * 4,
+    "forge_int8_conv_transpose2d_k2s2_forward": [_vp] * 5 + [_i] * 5 + [_vp, _vp],
     "forge_b200_set_dense_tile": [_i],
     "forge_b200_set_sparse_tile": [_i],
     "forge_b200_device_status": [_i],
@@ -72,7 +76,8 @@ def load():
             fn.restype = None
         elif name == "forge_b200_status_string":
             fn.restype = ctypes.c_char_p
-        elif name == "forge_w8a8_gated_mlp_workspace_bytes":
+        elif name in ("forge_w8a8_gated_mlp_workspace_bytes", "forge_int8_conv2d_workspace_size",
+                      "forge_int8_conv_transpose2d_k2s2_workspace_size"):
             fn.restype = ctypes.c_ulonglong
         else:
             fn.restype = ctypes.c_int

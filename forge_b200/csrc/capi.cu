@@ -2,6 +2,7 @@
 // (declared and cited in include/forge_b200.h). Thin argument adaptation only.
 #include "../../include/forge_b200.h"
 #include "common.cuh"
+#include "conv.cuh"
 #include "gemm_dense.cuh"
 #include "gemm_sparse.cuh"
 #include "gemm_fq.cuh"
@@ -286,6 +287,35 @@ int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, i
 int forge_prepare_weight(const void* weight, int weight_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta,
                          void* w_scale, int N, int K, forge_stream_t stream) {
     return prepare_weight(weight, weight_is_half, w_int8, W_comp, w_meta, H(w_scale), N, K, S(stream));
+}
+
+unsigned long long forge_int8_conv2d_workspace_size(int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                                                   int padW, int strideH, int strideW, int dilH, int dilW) {
+    return int8_conv2d_workspace_size(C_in, H, W, C_out, kH, kW, padH, padW, strideH, strideW, dilH, dilW);
+}
+
+int forge_int8_conv2d_forward(const void* input, const int8_t* weight, const void* w_scale, const void* bias,
+                              void* output, int N, int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                              int padW, int strideH, int strideW, int dilH, int dilW, void* workspace,
+                              forge_stream_t stream) {
+    (void)workspace;
+    return int8_conv2d_forward(static_cast<const __half*>(input), weight, static_cast<const __half*>(w_scale),
+                               static_cast<const __half*>(bias), static_cast<__half*>(output), N, C_in, H, W, C_out, kH, kW, padH,
+                               padW, strideH, strideW, dilH, dilW, S(stream));
+}
+
+unsigned long long forge_int8_conv_transpose2d_k2s2_workspace_size(int C_in, int H, int W, int C_out) {
+    return int8_conv_transpose2d_k2s2_workspace_size(C_in, H, W, C_out);
+}
+
+int forge_int8_conv_transpose2d_k2s2_forward(const void* input, const int8_t* weight, const void* w_scale,
+                                             const void* bias, void* output, int N, int C_in, int H, int W, int C_out,
+                                             void* workspace, forge_stream_t stream) {
+    (void)workspace;
+    return int8_conv_transpose2d_k2s2_forward(static_cast<const __half*>(input), weight,
+                                              static_cast<const __half*>(w_scale), static_cast<const __half*>(bias),
+                                              static_cast<__half*>(output), N, C_in, H, W, C_out,
+                                              S(stream));
 }
 
 void forge_b200_set_dense_tile(int bn) { g_force_dense_bn = bn; }

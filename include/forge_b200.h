@@ -210,6 +210,37 @@ int forge_pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, i
 int forge_prepare_weight(const void* weight, int weight_is_half, int8_t* w_int8, int8_t* W_comp, uint32_t* w_meta,
                          void* w_scale, int N, int K, forge_stream_t stream);
 
+/* ---------------------------------------------------------------- convolution callers of the GEMM */
+
+/* forge::nn::int8_conv2d_workspace_size - include/forge/nn/int8_conv2d.cuh:24-30,
+ * src/nn/int8_conv2d.cu:126-145. Returns the reference's figure so existing callers keep sizing
+ * their buffer the same way; forge_int8_conv2d_forward itself needs no scratch. */
+unsigned long long forge_int8_conv2d_workspace_size(int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                                                   int padW, int strideH, int strideW, int dilH, int dilW);
+
+/* forge::nn::int8_conv2d_forward - include/forge/nn/int8_conv2d.cuh:42-54, src/nn/int8_conv2d.cu:151-223.
+ * input (N,C_in,H,W) fp16 NCHW, weight (C_out, C_in*kH*kW) int8, w_scale (C_out) fp16, bias (C_out)
+ * fp16 or NULL, output (N,C_out,H_out,W_out) fp16. Each output position's patch is quantized per
+ * row exactly as the reference quantizes its im2col rows; one fused kernel over all samples.
+ * workspace is accepted for signature compatibility and may be NULL. */
+int forge_int8_conv2d_forward(const void* input, const int8_t* weight, const void* w_scale, const void* bias,
+                              void* output, int N, int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                              int padW, int strideH, int strideW, int dilH, int dilW, void* workspace,
+                              forge_stream_t stream);
+
+/* forge::nn::int8_conv_transpose2d_k2s2_workspace_size - include/forge/nn/int8_conv_transpose2d.cuh:25-26,
+ * src/nn/int8_conv_transpose2d.cu:103-117 (the reference's figure; no scratch is needed here). */
+unsigned long long forge_int8_conv_transpose2d_k2s2_workspace_size(int C_in, int H, int W, int C_out);
+
+/* forge::nn::int8_conv_transpose2d_k2s2_forward - include/forge/nn/int8_conv_transpose2d.cuh:40-49,
+ * src/nn/int8_conv_transpose2d.cu:123-191. 2x2 kernel, stride 2: input (N,C_in,H,W) fp16, weight
+ * (4*C_out, C_in) int8 with row co*4 + kh*2 + kw, w_scale / bias (C_out) fp16, output
+ * (N,C_out,2H,2W) fp16; the bias is added after the fp16 rounding of the scaled product, as the
+ * reference's scatter step does. workspace may be NULL. */
+int forge_int8_conv_transpose2d_k2s2_forward(const void* input, const int8_t* weight, const void* w_scale,
+                                             const void* bias, void* output, int N, int C_in, int H, int W, int C_out,
+                                             void* workspace, forge_stream_t stream);
+
 /* ---------------------------------------------------------------- diagnostics (additive) */
 
 /* Tuning/testing knobs: pin the dense tile width (64/128/256) or the sparse token-tile width

@@ -1,5 +1,5 @@
 // C++17 face of libforge_b200: the forge::gemm / forge::quant / forge::sparsity free functions
-// of Forge's quantized-inference path, with the reference's names, parameter order, defaults and
+// of Forge's quantized-inference path and the two forge::nn INT8 convolutions that call it, with the reference's names, parameter order, defaults and
 // void returns, implemented as inline forwards to the C ABI in forge_b200.h. Code written
 // against the reference headers (include/forge/{gemm,quant,sparsity}/*.cuh in the Forge tree)
 // compiles against this file unchanged and links with -lforge_b200.
@@ -14,6 +14,7 @@
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <cstddef>
 #include <cstdint>
 
 #include "forge_b200.h"
@@ -174,4 +175,37 @@ inline void sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, con
 }
 
 }  // namespace gemm
+
+namespace nn {
+
+// include/forge/nn/int8_conv2d.cuh:24-30
+inline size_t int8_conv2d_workspace_size(int C_in, int H, int W, int C_out, int kH, int kW, int padH, int padW,
+                                         int strideH, int strideW, int dilH = 1, int dilW = 1) {
+    return static_cast<size_t>(
+        forge_int8_conv2d_workspace_size(C_in, H, W, C_out, kH, kW, padH, padW, strideH, strideW, dilH, dilW));
+}
+
+// include/forge/nn/int8_conv2d.cuh:42-54
+inline void int8_conv2d_forward(const __half* input, const int8_t* weight, const __half* w_scale, const __half* bias,
+                                __half* output, int N, int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                                int padW, int strideH, int strideW, int dilH, int dilW, void* workspace,
+                                cudaStream_t stream = nullptr) {
+    b200::note(forge_int8_conv2d_forward(input, weight, w_scale, bias, output, N, C_in, H, W, C_out, kH, kW, padH, padW,
+                                         strideH, strideW, dilH, dilW, workspace, b200::st(stream)));
+}
+
+// include/forge/nn/int8_conv_transpose2d.cuh:25-26
+inline size_t int8_conv_transpose2d_k2s2_workspace_size(int C_in, int H, int W, int C_out) {
+    return static_cast<size_t>(forge_int8_conv_transpose2d_k2s2_workspace_size(C_in, H, W, C_out));
+}
+
+// include/forge/nn/int8_conv_transpose2d.cuh:40-49
+inline void int8_conv_transpose2d_k2s2_forward(const __half* input, const int8_t* weight, const __half* w_scale,
+                                               const __half* bias, __half* output, int N, int C_in, int H, int W,
+                                               int C_out, void* workspace, cudaStream_t stream = nullptr) {
+    b200::note(forge_int8_conv_transpose2d_k2s2_forward(input, weight, w_scale, bias, output, N, C_in, H, W, C_out,
+                                                        workspace, b200::st(stream)));
+}
+
+}  // namespace nn
 }  // namespace forge

@@ -23,6 +23,8 @@ REF_SOURCES = [
     "src/quant/quantize.cu", "src/quant/dequantize.cu",
     "src/sparsity/prune_compress.cu", "src/sparsity/pack_metadata.cu",
     "src/gemm/int8_dense.cu", "src/gemm/int8_sparse.cu",
+    "src/gemm/int8_gemm.cu", "src/gemm/int8_dp4a.cu",
+    "src/nn/int8_conv2d.cu", "src/nn/int8_conv_transpose2d.cu",
 ]
 
 

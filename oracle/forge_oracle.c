@@ -264,6 +264,88 @@ void oracle_sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_
     }
 }
 
+/* ---- INT8 convolution callers of the GEMM ------------------------------------------------
+ * src/nn/int8_conv2d.cu:41-80 (im2col with the row = one output position's patch, taps in
+ * (c, kh, kw) order, zero outside the image) and :165-221 (per sample: im2col -> per-row
+ * quantize -> GEMM + dequant + bias -> transpose to NCHW). The column matrix here holds all
+ * samples one after the other: row = n * H_out * W_out + position. ---- */
+static int conv_out_size(int in, int pad, int dil, int k, int stride) {
+    return (in + 2 * pad - dil * (k - 1) - 1) / stride + 1;
+}
+
+void oracle_im2col(const uint16_t* input, uint16_t* col, int N, int C_in, int H, int W, int kH, int kW, int padH,
+                   int padW, int strideH, int strideW, int dilH, int dilW) {
+    const int H_out = conv_out_size(H, padH, dilH, kH, strideH);
+    const int W_out = conv_out_size(W, padW, dilW, kW, strideW);
+    const int K = C_in * kH * kW;
+    const long long rows = (long long)N * H_out * W_out;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < rows; r++) {
+        const int n = (int)(r / ((long long)H_out * W_out));
+        const int sp = (int)(r % ((long long)H_out * W_out));
+        const int ho = sp / W_out, wo = sp % W_out;
+        const uint16_t* in_n = input + (size_t)n * C_in * H * W;
+        uint16_t* dst = col + (size_t)r * K;
+        int k = 0;
+        for (int c = 0; c < C_in; c++)
+            for (int kh = 0; kh < kH; kh++)
+                for (int kw = 0; kw < kW; kw++, k++) {
+                    const int h = ho * strideH + kh * dilH - padH;
+                    const int w = wo * strideW + kw * dilW - padW;
+                    dst[k] = (h >= 0 && h < H && w >= 0 && w < W) ? in_n[((size_t)c * H + h) * W + w] : 0;
+                }
+    }
+}
+
+/* GEMM output (N*HW, C_out) fp16 -> NCHW; src/nn/int8_conv2d.cu:107-119 per sample. */
+void oracle_rows_to_nchw(const uint16_t* gemm_out, uint16_t* output, int N, int HW, int C_out) {
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++)
+        for (int s = 0; s < HW; s++)
+            for (int c = 0; c < C_out; c++)
+                output[((size_t)n * C_out + c) * HW + s] = gemm_out[((size_t)n * HW + s) * C_out + c];
+}
+
+/* Whole conv on the CPU with this file's quantizer (so +-1 int8 step from the GPU quantizer). */
+void oracle_int8_conv2d(const uint16_t* input, const int8_t* weight, const uint16_t* w_scale, const uint16_t* bias,
+                        uint16_t* output, int N, int C_in, int H, int W, int C_out, int kH, int kW, int padH, int padW,
+                        int strideH, int strideW, int dilH, int dilW) {
+    const int H_out = conv_out_size(H, padH, dilH, kH, strideH);
+    const int W_out = conv_out_size(W, padW, dilW, kW, strideW);
+    const int K = C_in * kH * kW;
+    const long long rows = (long long)N * H_out * W_out;
+    uint16_t* col = (uint16_t*)malloc((size_t)rows * K * 2);
+    int8_t* q = (int8_t*)malloc((size_t)rows * K);
+    float* as = (float*)malloc((size_t)rows * 4);
+    int32_t* acc = (int32_t*)malloc((size_t)rows * C_out * 4);
+    uint16_t* g = (uint16_t*)malloc((size_t)rows * C_out * 2);
+    oracle_im2col(input, col, N, C_in, H, W, kH, kW, padH, padW, strideH, strideW, dilH, dilW);
+    oracle_quantize(col, q, as, (int)rows, K);
+    oracle_int8_gemm_s32(q, weight, acc, (int)rows, K, C_out);
+    oracle_dequantize_gemm_epilogue(acc, as, w_scale, bias, g, (int)rows, C_out);
+    oracle_rows_to_nchw(g, output, N, H_out * W_out, C_out);
+    free(col); free(q); free(as); free(acc); free(g);
+}
+
+/* 2x2 stride-2 transposed conv, scatter step; src/nn/int8_conv_transpose2d.cu:70-101: GEMM output
+ * (N*H*W, 4*C_out) fp16 computed with the channel scale replicated 4x and NO bias; column
+ * n = co*4 + kh*2 + kw goes to output pixel (2h+kh, 2w+kw) of channel co; the bias is added in fp32
+ * to the already rounded fp16 value and the sum is rounded to fp16 again. */
+void oracle_conv_transpose_k2s2_scatter(const uint16_t* gemm_out, const uint16_t* bias, uint16_t* output, int N,
+                                        int H, int W, int C_out) {
+    const int Ng = 4 * C_out;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++)
+        for (int h = 0; h < H; h++)
+            for (int w = 0; w < W; w++)
+                for (int j = 0; j < Ng; j++) {
+                    const int co = j / 4, kh = (j % 4) / 2, kw = j % 2;
+                    float v = half_to_float(gemm_out[(((size_t)n * H + h) * W + w) * Ng + j]);
+                    if (bias) v = v + half_to_float(bias[co]);
+                    output[(((size_t)n * C_out + co) * 2 * H + 2 * h + kh) * 2 * W + 2 * w + kw] = float_to_half(v);
+                }
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

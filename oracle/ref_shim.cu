@@ -4,6 +4,8 @@
 // the reference source tree is present; loaded only by tests/ and bench.py's comparison legs.
 #include <forge/gemm/int8_dense.cuh>
 #include <forge/gemm/int8_sparse.cuh>
+#include <forge/nn/int8_conv2d.cuh>
+#include <forge/nn/int8_conv_transpose2d.cuh>
 #include <forge/quant/dequantize.cuh>
 #include <forge/quant/quantize.cuh>
 #include <forge/sparsity/pack_metadata.cuh>
@@ -53,6 +55,29 @@ void ref_prune_compress_24(const int8_t* w, int8_t* c, uint8_t* m, int N, int K,
 }
 void ref_pack_metadata(const uint8_t* raw, uint32_t* packed, int N, int K, void* stream) {
     forge::sparsity::pack_metadata(raw, packed, N, K, (cudaStream_t)stream);
+}
+
+// The two in-library callers of the INT8 GEMM (src/nn/int8_conv2d.cu, src/nn/int8_conv_transpose2d.cu).
+unsigned long long ref_int8_conv2d_workspace_size(int C_in, int H, int W, int C_out, int kH, int kW, int padH, int padW,
+                                                  int strideH, int strideW, int dilH, int dilW) {
+    return forge::nn::int8_conv2d_workspace_size(C_in, H, W, C_out, kH, kW, padH, padW, strideH, strideW, dilH, dilW);
+}
+void ref_int8_conv2d_forward(const void* input, const int8_t* weight, const void* w_scale, const void* bias,
+                             void* output, int N, int C_in, int H, int W, int C_out, int kH, int kW, int padH,
+                             int padW, int strideH, int strideW, int dilH, int dilW, void* workspace, void* stream) {
+    forge::nn::int8_conv2d_forward((const __half*)input, weight, (const __half*)w_scale, (const __half*)bias,
+                                   (__half*)output, N, C_in, H, W, C_out, kH, kW, padH, padW, strideH, strideW, dilH,
+                                   dilW, workspace, (cudaStream_t)stream);
+}
+unsigned long long ref_int8_conv_transpose2d_k2s2_workspace_size(int C_in, int H, int W, int C_out) {
+    return forge::nn::int8_conv_transpose2d_k2s2_workspace_size(C_in, H, W, C_out);
+}
+void ref_int8_conv_transpose2d_k2s2_forward(const void* input, const int8_t* weight, const void* w_scale,
+                                            const void* bias, void* output, int N, int C_in, int H, int W, int C_out,
+                                            void* workspace, void* stream) {
+    forge::nn::int8_conv_transpose2d_k2s2_forward((const __half*)input, weight, (const __half*)w_scale,
+                                                  (const __half*)bias, (__half*)output, N, C_in, H, W, C_out,
+                                                  workspace, (cudaStream_t)stream);
 }
 
 }  // extern "C"

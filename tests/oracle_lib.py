@@ -38,6 +38,10 @@ def oracle():
         lib.oracle_float_to_half.restype = ctypes.c_uint16
         lib.oracle_half_to_float.argtypes = [ctypes.c_uint16]
         lib.oracle_half_to_float.restype = ctypes.c_float
+        lib.oracle_im2col.argtypes = [_vp, _vp] + [_i] * 12
+        lib.oracle_rows_to_nchw.argtypes = [_vp, _vp, _i, _i, _i]
+        lib.oracle_int8_conv2d.argtypes = [_vp] * 5 + [_i] * 13
+        lib.oracle_conv_transpose_k2s2_scatter.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i]
         lib.oracle_num_threads.restype = _i
         _oracle = lib
     return _oracle
@@ -134,6 +138,47 @@ def sparse_gemm_s32(W_comp, x, w_meta):
     return out
 
 
+def conv_out_size(size, pad, dil, k, stride):
+    return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+
+def im2col(x_f16, kH, kW, padH, padW, strideH, strideW, dilH, dilW):
+    """(N,C,H,W) fp16 -> (N*H_out*W_out, C*kH*kW) fp16, the reference's patch-per-row layout."""
+    x = _c(x_f16, np.float16)
+    N, C, H, W = x.shape
+    Ho, Wo = conv_out_size(H, padH, dilH, kH, strideH), conv_out_size(W, padW, dilW, kW, strideW)
+    col = np.empty((N * Ho * Wo, C * kH * kW), np.float16)
+    oracle().oracle_im2col(_p(x), _p(col), N, C, H, W, kH, kW, padH, padW, strideH, strideW, dilH, dilW)
+    return col, Ho, Wo
+
+
+def rows_to_nchw(g_f16, N, HW, C_out):
+    g = _c(g_f16, np.float16)
+    out = np.empty((N, C_out, HW), np.float16)
+    oracle().oracle_rows_to_nchw(_p(g), _p(out), N, HW, C_out)
+    return out
+
+
+def int8_conv2d(x_f16, weight, w_scale, bias, kH, kW, padH, padW, strideH, strideW, dilH, dilW):
+    x, weight, w_scale = _c(x_f16, np.float16), _c(weight, np.int8), _c(w_scale, np.float16)
+    bias = None if bias is None else _c(bias, np.float16)
+    N, C, H, W = x.shape
+    C_out = weight.shape[0]
+    Ho, Wo = conv_out_size(H, padH, dilH, kH, strideH), conv_out_size(W, padW, dilW, kW, strideW)
+    out = np.empty((N, C_out, Ho, Wo), np.float16)
+    oracle().oracle_int8_conv2d(_p(x), _p(weight), _p(w_scale), _p(bias), _p(out), N, C, H, W, C_out, kH, kW, padH,
+                                padW, strideH, strideW, dilH, dilW)
+    return out
+
+
+def conv_transpose_k2s2_scatter(g_f16, bias, N, H, W, C_out):
+    g = _c(g_f16, np.float16)
+    bias = None if bias is None else _c(bias, np.float16)
+    out = np.empty((N, C_out, 2 * H, 2 * W), np.float16)
+    oracle().oracle_conv_transpose_k2s2_scatter(_p(g), _p(bias), _p(out), N, H, W, C_out)
+    return out
+
+
 # --------------------------------------------------------------------------------------------
 # Reference GPU kernels (oracle/_ref). Arguments are torch CUDA tensors.
 
@@ -154,6 +199,14 @@ def ref():
         lib.ref_sparse_int8_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i]
         lib.ref_prune_compress_24.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         lib.ref_pack_metadata.argtypes = [_vp, _vp, _i, _i, _vp]
+        lib.ref_int8_conv2d_workspace_size.argtypes = [_i] * 12
+        lib.ref_int8_conv2d_workspace_size.restype = ctypes.c_ulonglong
+        lib.ref_int8_conv2d_forward.argtypes = [_vp] * 5 + [_i] * 13 + [_vp, _vp]
+        lib.ref_int8_conv2d_forward.restype = None
+        lib.ref_int8_conv_transpose2d_k2s2_workspace_size.argtypes = [_i] * 4
+        lib.ref_int8_conv_transpose2d_k2s2_workspace_size.restype = ctypes.c_ulonglong
+        lib.ref_int8_conv_transpose2d_k2s2_forward.argtypes = [_vp] * 5 + [_i] * 5 + [_vp, _vp]
+        lib.ref_int8_conv_transpose2d_k2s2_forward.restype = None
         for name in ("ref_fused_quantize_activation", "ref_quantize_two_pass", "ref_fused_dequantize_bias",
                      "ref_int8_gemm_dequant", "ref_int8_linear", "ref_sparse_int8_gemm", "ref_sparse_int8_linear",
                      "ref_prune_compress_24", "ref_pack_metadata"):
@@ -217,3 +270,30 @@ def ref_prune_pack(w):
     ref().ref_prune_compress_24(tp(w), tp(comp), tp(raw), N, K, cur_stream())
     ref().ref_pack_metadata(tp(raw), tp(packed), N, K, cur_stream())
     return comp, raw, packed
+
+
+def ref_int8_conv2d(x, weight, w_scale, bias, kH, kW, padH, padW, strideH, strideW, dilH, dilW):
+    import torch
+    N, C, H, W = x.shape
+    C_out = weight.shape[0]
+    Ho, Wo = conv_out_size(H, padH, dilH, kH, strideH), conv_out_size(W, padW, dilW, kW, strideW)
+    out = torch.empty((N, C_out, Ho, Wo), dtype=torch.float16, device=x.device)
+    ws = torch.empty(int(ref().ref_int8_conv2d_workspace_size(C, H, W, C_out, kH, kW, padH, padW, strideH, strideW,
+                                                              dilH, dilW)) + 16, dtype=torch.uint8, device=x.device)
+    ref().ref_int8_conv2d_forward(tp(x), tp(weight), tp(w_scale), tp(bias), tp(out), N, C, H, W, C_out, kH, kW, padH,
+                                  padW, strideH, strideW, dilH, dilW, tp(ws), cur_stream())
+    torch.cuda.synchronize()
+    return out
+
+
+def ref_int8_conv_transpose2d_k2s2(x, weight, w_scale, bias):
+    import torch
+    N, C, H, W = x.shape
+    C_out = weight.shape[0] // 4
+    out = torch.empty((N, C_out, 2 * H, 2 * W), dtype=torch.float16, device=x.device)
+    ws = torch.empty(int(ref().ref_int8_conv_transpose2d_k2s2_workspace_size(C, H, W, C_out)) + 16, dtype=torch.uint8,
+                     device=x.device)
+    ref().ref_int8_conv_transpose2d_k2s2_forward(tp(x), tp(weight), tp(w_scale), tp(bias), tp(out), N, C, H, W, C_out,
+                                                 tp(ws), cur_stream())
+    torch.cuda.synchronize()
+    return out
