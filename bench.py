@@ -391,6 +391,29 @@ def run_case(args):
             # minimum traffic: read x (fp16) and the compressed weight once, write the fp16 output
             work, unit, bound = (2.0 * m * k + 0.625 * n * k + 2.0 * m * n) / 1e9, "GB/s", "hbm"
             shape = {"M": m, "K": k, "N": n}
+        elif name in ("conv", "conv_transpose"):
+            # INT8 conv2d 3x3 pad 1 (or the 2x2 stride-2 transposed conv) on a frame: --m = batch,
+            # --k = C_in, --n = C_out, --height / --width
+            nb, ci, co = args.m or 1, args.k or 16, args.n or 32
+            hh, ww = args.height, args.width
+            x = torch.randn((nb, ci, hh, ww), generator=g, device=dev, dtype=torch.float16)
+            w_s = (torch.rand(co, generator=g, device=dev) * 0.02 + 0.001).half()
+            bias = (torch.randn(co, generator=g, device=dev) * 0.01).half()
+            if name == "conv":
+                wq = ri8(co, ci * 9)
+                out = torch.empty((nb, co, hh, ww), dtype=torch.float16, device=dev)
+                fn = lambda: lib.forge_int8_conv2d_forward(x.data_ptr(), wq.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
+                                                           out.data_ptr(), nb, ci, hh, ww, co, 3, 3, 1, 1, 1, 1, 1, 1, 0,
+                                                           S[0])
+            else:
+                wq = ri8(4 * co, ci)
+                out = torch.empty((nb, co, 2 * hh, 2 * ww), dtype=torch.float16, device=dev)
+                fn = lambda: lib.forge_int8_conv_transpose2d_k2s2_forward(x.data_ptr(), wq.data_ptr(), w_s.data_ptr(),
+                                                                          bias.data_ptr(), out.data_ptr(), nb, ci, hh,
+                                                                          ww, co, 0, S[0])
+            # minimum traffic: the input and the weight read once, the output written once
+            work, unit, bound = (2.0 * x.numel() + wq.numel() + 2.0 * out.numel()) / 1e9, "GB/s", "hbm"
+            shape = {"N": nb, "C_in": ci, "H": hh, "W": ww, "C_out": co}
         elif name in ("mlp", "mlp_sparse"):
             # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
             m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
@@ -556,7 +579,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="headline",
                     help="headline (the contract line) or one kernel: dense, dense_s32, sparse, sparse_s32, "
-                         "quantize, dequant, prune, pack, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn)")
+                         "quantize, dequant, prune, pack, conv, conv_transpose, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn)")
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -566,6 +589,8 @@ def main():
     ap.add_argument("--reps", type=int, default=1,
                     help="--case runs: back-to-back calls per timed region (hides host launch latency of "
                          "microsecond-sized kernels; inputs then stay in L2 after the first call)")
+    ap.add_argument("--height", type=int, default=1080, help="conv cases: input height")
+    ap.add_argument("--width", type=int, default=1920, help="conv cases: input width")
     ap.add_argument("--rotate", type=int, default=1,
                     help="--case runs with --graph: number of separate operand sets the captured calls cycle through "
                          "(sets x bytes per set above the L2 size makes every call read from HBM)")

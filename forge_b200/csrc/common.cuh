@@ -159,9 +159,9 @@ inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, con
                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
     struct Key {
         const void* base;
-        uint64_t dims[3];
-        uint64_t strides[2];
-        uint32_t box[3];
+        uint64_t dims[4];
+        uint64_t strides[3];
+        uint32_t box[4];
         int dtype, rank, swizzle;
     };
     struct Entry {
@@ -183,7 +183,8 @@ inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, con
     for (int i = 0; i + 1 < rank; i++) k.strides[i] = strides_bytes[i];
     uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
     h ^= (k.dims[0] * 31 + k.dims[1]) * 0xC2B2AE3D27D4EB4Full + k.box[0] * 131 + k.box[1] * 17 + k.box[2] +
-         (uint64_t)k.swizzle * 7 + (uint64_t)k.dtype * 3 + k.dims[2] * 1315423911ull;
+         (uint64_t)k.swizzle * 7 + (uint64_t)k.dtype * 3 + k.dims[2] * 1315423911ull + k.dims[3] * 2654435761ull +
+         k.box[3] * 977;
     Entry& e = cache[(h >> 32) % kSlots];
     if (e.valid && memcmp(&e.key, &k, sizeof(Key)) == 0) {
         *out = e.map;
@@ -191,10 +192,10 @@ inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, con
     }
     PFN_encodeTiled fn = get_encode_fn();
     if (fn == nullptr) return false;
-    cuuint64_t gdim[3];
-    cuuint64_t gstr[2];
-    cuuint32_t bx[3];
-    cuuint32_t es[3] = {1, 1, 1};
+    cuuint64_t gdim[4];
+    cuuint64_t gstr[3];
+    cuuint32_t bx[4];
+    cuuint32_t es[4] = {1, 1, 1, 1};
     for (int i = 0; i < rank; i++) {
         gdim[i] = dims[i];
         bx[i] = box[i];

@@ -49,11 +49,23 @@ struct ConvShape {
     int ct;                   // columns per CTA (multiple of 16, <= 256)
     int tmem_cols;            // power of two >= max(32, ct)
     int b_by_tma;
+    int stages;               // ring depth: min(kStages, 128-tap slabs per patch)
+    // input-tile variant: the CTA's positions form a TH x TW block of one sample's output grid and the
+    // input window they read (all channels) is brought into shared memory by one TMA load
+    int TW, tw_log2, TH, tiles_w, tiles_h;
+    int IH, IWp;              // window rows; row pitch in elements (multiple of 8)
+    int xoff;                 // window column of the first tap of position (.,0): the load starts 16-byte aligned
+    int in_off, in_bytes;     // window's place in shared memory
 };
 
 __device__ __forceinline__ uint32_t pack4(int q0, int q1, int q2, int q3) {
     return (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
            ((uint32_t)(q3 & 0xFF) << 24);
+}
+
+// The quantizer's value step; the byte in the low 8 bits.
+__device__ __forceinline__ uint32_t quant_byte(float x, float inv_scale) {
+    return static_cast<uint32_t>(quant_value(x, inv_scale)) & 0xFFu;
 }
 
 // Walks the taps of one patch in (c, kh, kw) order.
@@ -83,27 +95,40 @@ __device__ __forceinline__ float load_tap(const __half* __restrict__ in_n, const
 // MODE 0: conv2d, NCHW output. MODE 1: 2x2 stride-2 transposed conv, GEMM column n = co*4 + kh*2 + kw
 // scattered to output pixel (2h+kh, 2w+kw), bias added after the fp16 rounding of the GEMM result
 // as the reference's scatter kernel does.
-template <int MODE>
-__global__ void __launch_bounds__(kThreads)
-conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const ConvShape s, const __half* __restrict__ input,
+// T: taps per channel (kH * kW) known at compile time - 1, 4 or 9 - or 0 for any other kernel size.
+// HALO: input-tile variant (needs T > 0); otherwise taps are read from global memory.
+template <int MODE, int T, bool HALO>
+__global__ void __launch_bounds__(kThreads, HALO ? 4 : 3)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_in,
+                  const ConvShape s, const __half* __restrict__ input,
                   const int8_t* __restrict__ weight, const __half* __restrict__ w_scale,
                   const __half* __restrict__ bias, __half* __restrict__ output, int* __restrict__ status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int stage_bytes = kABytes + s.ct * 128;
-    float* s_ws = reinterpret_cast<float*>(smem + kStages * stage_bytes);   // [ct] weight scales
+    float* s_ws = reinterpret_cast<float*>(smem + s.stages * stage_bytes);   // [ct] weight scales
     float* s_bias = s_ws + 256;                                             // [ct]
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + 256);
     uint64_t* full_bar = bars;                 // [kStages]: 4 gather warps + the weight loader
     uint64_t* empty_bar = bars + kStages;      // [kStages]: the MMA commit
     uint64_t* tmem_full = bars + 2 * kStages;  // [1]
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    uint64_t* in_full = tmem_full + 1;         // [1]: the input window has landed
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(in_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    const __half* in_tile = reinterpret_cast<const __half*>(smem + s.in_off);
 
     const int warp_id = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicExch(status, 600);
         return;
+    }
+    // position block of this CTA (HALO): sample, block row, block column
+    int t_smp = 0, t_bh = 0, t_bw = 0;
+    if (HALO) {
+        t_bw = blockIdx.x % s.tiles_w;
+        const int rest = blockIdx.x / s.tiles_w;
+        t_bh = rest % s.tiles_h;
+        t_smp = rest / s.tiles_h;
     }
     const int n0 = blockIdx.y * s.ct;            // first GEMM column of this CTA
     const int num_kb = (s.K + 127) / 128;
@@ -115,10 +140,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const ConvShape s, c
             mbar_init(&empty_bar[i], 1);
         }
         mbar_init(tmem_full, 1);
+        mbar_init(in_full, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp_id == 4 && lane == 0 && s.b_by_tma) prefetch_tensormap(&tm_b);
+    if (warp_id == 4 && lane == 0) {
+        if (s.b_by_tma) prefetch_tensormap(&tm_b);
+        if (HALO) prefetch_tensormap(&tm_in);
+    }
     if (warp_id == 5) {
         tmem_alloc(tmem_base_slot, s.tmem_cols);
         tmem_relinquish();
@@ -136,59 +165,182 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const ConvShape s, c
 
     if (warp_id < 4) {
         // ------------------------------------------------------------ gather + quantize, then epilogue
-        const long long m = (long long)blockIdx.x * kRows + threadIdx.x;
-        const bool valid = m < s.rows;
+        bool valid;
+        int smp, sp, ho, wo;
         const int hw_out = s.H_out * s.W_out;
-        const int smp = valid ? (int)(m / hw_out) : 0;
-        const int sp = valid ? (int)(m - (long long)smp * hw_out) : 0;
-        const int ho = sp / s.W_out, wo = sp - ho * s.W_out;
+        if (HALO) {
+            ho = t_bh * s.TH + (threadIdx.x >> s.tw_log2);
+            wo = t_bw * s.TW + (threadIdx.x & (s.TW - 1));
+            valid = ho < s.H_out && wo < s.W_out;
+            smp = t_smp;
+            sp = ho * s.W_out + wo;
+        } else {
+            const long long m = (long long)blockIdx.x * kRows + threadIdx.x;
+            valid = m < s.rows;
+            smp = valid ? (int)(m / hw_out) : 0;
+            sp = valid ? (int)(m - (long long)smp * hw_out) : 0;
+            ho = sp / s.W_out;
+            wo = sp - ho * s.W_out;
+        }
         const int h0 = ho * s.strideH - s.padH, w0 = wo * s.strideW - s.padW;
         const __half* in_n = input + (size_t)smp * s.C_in * s.H * s.W;
 
-        float amax = 0.f;
-        TapWalker tw;
-        if (valid) {
-            tw.reset();
-            for (int k = 0; k < s.K; k++, tw.next(s)) amax = max_ftz(amax, abs_ftz(load_tap(in_n, s, tw, h0, w0)));
-        }
-        float scale, inv;
-        quant_scale(amax, scale, inv);
-
-        tw.reset();
         const int r = threadIdx.x;
         bool ok = true;
-        for (int kb = 0; kb < num_kb; kb++) {
-            const int stage = kb % kStages;
-            const uint32_t phase = (kb / kStages) & 1;
-            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {
-                atomicExch(status, 601);
-                ok = false;
-                break;
-            }
-            uint8_t* sa = smem + stage * stage_bytes + r * 128;
-            int k = kb * 128;
-#pragma unroll 1
-            for (int ch = 0; ch < 8; ch++) {
-                uint32_t p[4] = {0u, 0u, 0u, 0u};
-                if (valid && k < s.K) {
-                    int q[16];
+        float scale, inv;
+        if (T > 0) {
+            // ---- fast path: the T tap offsets and their in-image flags are per-thread constants
+            constexpr int G = (T == 1) ? 16 : (T == 4) ? 8 : 4;   // channels per group: ~32 loads in flight
+            int off[T > 0 ? T : 1];
+            uint32_t inside = 0;
+            size_t plane;
+            const __half* pc0;
+            if (HALO) {
+                // window-relative offsets; the TMA load zero-filled everything outside the image
+                const int base = (threadIdx.x >> s.tw_log2) * s.strideH * s.IWp + (threadIdx.x & (s.TW - 1)) * s.strideW +
+                                 s.xoff;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        q[j] = 0;
-                        if (k + j < s.K) {
-                            q[j] = quant_value(load_tap(in_n, s, tw, h0, w0), inv);
-                            tw.next(s);
+                for (int j = 0; j < T; j++) {
+                    const int kh = j / s.kW, kw = j - kh * s.kW;
+                    off[j] = base + kh * s.dilH * s.IWp + kw * s.dilW;
+                }
+                inside = 0xFFFFFFFFu;
+                plane = (size_t)s.IH * s.IWp;
+                pc0 = in_tile;
+                if (!__all_sync(0xffffffffu, mbar_wait(in_full, 0, abort_flag))) {
+                    atomicExch(status, 605);
+                    ok = false;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < T; j++) {
+                    const int kh = j / s.kW, kw = j - kh * s.kW;
+                    const int h = h0 + kh * s.dilH, w = w0 + kw * s.dilW;
+                    const bool in = valid && (unsigned)h < (unsigned)s.H && (unsigned)w < (unsigned)s.W;
+                    off[j] = in ? h * s.W + w : 0;
+                    inside |= in ? (1u << j) : 0u;
+                }
+                plane = (size_t)s.H * s.W;
+                pc0 = in_n;
+            }
+            auto tap = [&](const __half* p, int j) -> float {
+                if (HALO) return __half2float(p[off[j]]);
+                return ((inside >> j) & 1u) ? __half2float(__ldg(p + off[j])) : 0.f;
+            };
+            float amax = 0.f;
+            if (ok) {
+                const __half* pc = pc0;
+#pragma unroll G
+                for (int c = 0; c < s.C_in; c++, pc += plane) {
+#pragma unroll
+                    for (int j = 0; j < T; j++) amax = max_ftz(amax, abs_ftz(tap(pc, j)));
+                }
+            }
+            quant_scale(amax, scale, inv);
+
+            // pass 2: G channels = G*T taps = G*T/4 whole 32-bit words of the patch row at a time
+            int wi = 0;                 // word index within the patch row; 32 words = one 128-tap stage
+            uint8_t* rowp = nullptr;
+            auto emit = [&](uint32_t word) {
+                if (!ok) return;
+                if ((wi & 31) == 0) {
+                    const int kb = wi >> 5;
+                    const int stage = kb % s.stages;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], ((kb / s.stages) & 1) ^ 1, abort_flag))) {
+                        atomicExch(status, 601);
+                        ok = false;
+                        return;
+                    }
+                    rowp = smem + stage * stage_bytes + r * 128;
+                }
+                *reinterpret_cast<uint32_t*>(rowp + ((((wi >> 2) & 7) ^ (r & 7)) << 4) + ((wi & 3) << 2)) = word;
+                if ((wi & 31) == 31) {
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_bar[(wi >> 5) % s.stages]);
+                }
+                wi++;
+            };
+            const __half* pc = pc0;
+            int c = 0;
+            for (; c + G <= s.C_in; c += G, pc += G * plane) {
+                uint32_t q[G * (T > 0 ? T : 1)];
+#pragma unroll
+                for (int cc = 0; cc < G; cc++) {
+#pragma unroll
+                    for (int j = 0; j < T; j++) {
+                        q[cc * T + j] = quant_byte(tap(pc + cc * plane, j), inv);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < G * T / 4; i++)
+                    emit(q[4 * i] | (q[4 * i + 1] << 8) | (q[4 * i + 2] << 16) | (q[4 * i + 3] << 24));
+            }
+            {   // leftover channels (fewer than G): bytes collected with a running shift
+                uint32_t word = 0;
+                int nb = 0;
+                for (; c < s.C_in; c++, pc += plane) {
+#pragma unroll
+                    for (int j = 0; j < T; j++) {
+                        word |= quant_byte(tap(pc, j), inv) << (8 * nb);
+                        if (++nb == 4) {
+                            emit(word);
+                            word = 0;
+                            nb = 0;
                         }
                     }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) p[j] = pack4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
                 }
-                k += 16;
-                *reinterpret_cast<uint4*>(sa + ((ch ^ (r & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+                if (nb != 0) emit(word);
             }
-            fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_bar[stage]);
+            // a last stage that is not full: taps past K meet zero weights, whatever is in them
+            if (ok && (wi & 31) != 0) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_bar[(wi >> 5) % s.stages]);
+            }
+        } else {
+            float amax = 0.f;
+            TapWalker tw;
+            if (valid) {
+                tw.reset();
+                for (int k = 0; k < s.K; k++, tw.next(s)) amax = max_ftz(amax, abs_ftz(load_tap(in_n, s, tw, h0, w0)));
+            }
+            quant_scale(amax, scale, inv);
+
+            tw.reset();
+            for (int kb = 0; kb < num_kb; kb++) {
+                const int stage = kb % s.stages;
+                const uint32_t phase = (kb / s.stages) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {
+                    atomicExch(status, 601);
+                    ok = false;
+                    break;
+                }
+                uint8_t* sa = smem + stage * stage_bytes + r * 128;
+                int k = kb * 128;
+#pragma unroll 1
+                for (int ch = 0; ch < 8; ch++) {
+                    uint32_t p[4] = {0u, 0u, 0u, 0u};
+                    if (valid && k < s.K) {
+                        int q[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            q[j] = 0;
+                            if (k + j < s.K) {
+                                q[j] = quant_value(load_tap(in_n, s, tw, h0, w0), inv);
+                                tw.next(s);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) p[j] = pack4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+                    }
+                    k += 16;
+                    *reinterpret_cast<uint4*>(sa + ((ch ^ (r & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+                }
+                fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_bar[stage]);
+            }
         }
 
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tmem_full, 0, abort_flag));
@@ -239,11 +391,16 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const ConvShape s, c
             tc_fence_before();
         }
     } else if (warp_id == 4) {
-        // ------------------------------------------------------------ weight tiles
+        // ------------------------------------------------------------ input window, weight tiles
+        if (HALO && lane == 0) {
+            mbar_expect_tx(in_full, s.in_bytes);
+            tma_load_4d(smem + s.in_off, &tm_in, in_full, t_bw * s.TW * s.strideW - s.padW - s.xoff,
+                        t_bh * s.TH * s.strideH - s.padH, 0, t_smp);
+        }
         bool ok = true;
         for (int kb = 0; kb < num_kb && ok; kb++) {
-            const int stage = kb % kStages;
-            const uint32_t phase = (kb / kStages) & 1;
+            const int stage = kb % s.stages;
+            const uint32_t phase = (kb / s.stages) & 1;
             uint8_t* sb = smem + stage * stage_bytes + kABytes;
             if (s.b_by_tma) {
                 if (lane == 0) {
@@ -286,8 +443,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const ConvShape s, c
             const uint32_t idesc = make_idesc_i8(kRows, s.ct, false);
             bool ok = true;
             for (int kb = 0; kb < num_kb; kb++) {
-                const int stage = kb % kStages;
-                const uint32_t phase = (kb / kStages) & 1;
+                const int stage = kb % s.stages;
+                const uint32_t phase = (kb / s.stages) & 1;
                 if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                     atomicExch(status, 604);
                     ok = false;
@@ -327,7 +484,29 @@ inline int conv_out_size(int in, int pad, int dil, int k, int stride) {
     return (in + 2 * pad - dil * (k - 1) - 1) / stride + 1;
 }
 
-template <int MODE>
+constexpr int kMiscBytes = 2 * 256 * (int)sizeof(float) + 128;   // scales, bias, barriers
+constexpr int kMaxSmem = 227 * 1024;
+
+template <int MODE, int T, bool HALO>
+int launch_kernel(const ConvShape& s, const CUtensorMap& tm_b, const CUtensorMap& tm_in, int smem, dim3 grid,
+                  const __half* input, const int8_t* weight, const __half* w_scale, const __half* bias,
+                  __half* output, cudaStream_t stream) {
+    static int attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = conv_igemm_kernel<MODE, T, HALO>;
+    if (!attr_set[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess)
+            return kLaunchFailed;
+        attr_set[dev & 63] = 1;
+    }
+    int* status = status_word();
+    if (status == nullptr) return kLaunchFailed;
+    kern<<<grid, kThreads, smem, stream>>>(tm_b, tm_in, s, input, weight, w_scale, bias, output, status);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+template <int MODE, int T>
 int launch_conv(ConvShape s, const __half* input, const int8_t* weight, const __half* w_scale, const __half* bias,
                 __half* output, cudaStream_t stream) {
     if (!device_is_sm100()) return kUnsupportedArch;
@@ -343,35 +522,59 @@ int launch_conv(ConvShape s, const __half* input, const int8_t* weight, const __
     s.tmem_cols = 32;
     while (s.tmem_cols < s.ct) s.tmem_cols *= 2;
     s.b_by_tma = (s.K % 16 == 0 && aligned16(weight)) ? 1 : 0;
+    s.stages = std::min(kStages, (s.K + 127) / 128);
+    const int ring_bytes = s.stages * (kABytes + s.ct * 128);
 
-    CUtensorMap tm_b;
+    CUtensorMap tm_b, tm_in;
+    memset(&tm_b, 0, sizeof(tm_b));
+    memset(&tm_in, 0, sizeof(tm_in));
     if (s.b_by_tma) {
         const uint64_t dims[2] = {(uint64_t)s.K, (uint64_t)s.cols};
         const uint64_t str[1] = {(uint64_t)s.K};
         const uint32_t box[2] = {128, (uint32_t)s.ct};
         if (!make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
-    } else {
-        memset(&tm_b, 0, sizeof(tm_b));
     }
-    const int smem = kStages * (kABytes + s.ct * 128) + 2 * 256 * (int)sizeof(float) + 128;
-    static int attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    auto kern = conv_igemm_kernel<MODE>;
-    if (!attr_set[dev & 63]) {
-        const int max_smem = kStages * (kABytes + 256 * 128) + 2 * 256 * (int)sizeof(float) + 128;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
-            return kLaunchFailed;
-        attr_set[dev & 63] = 1;
+
+    // Input-tile variant: TH x TW position blocks whose input window (all channels) is one TMA box.
+    bool halo = false;
+    if (T > 0 && s.W % 8 == 0 && aligned16(input) && s.C_in <= 256) {
+        s.TW = (s.W_out >= 24) ? 32 : (s.W_out >= 12) ? 16 : 8;
+        s.tw_log2 = (s.TW == 32) ? 5 : (s.TW == 16) ? 4 : 3;
+        s.TH = kRows / s.TW;
+        s.tiles_w = (s.W_out + s.TW - 1) / s.TW;
+        s.tiles_h = (s.H_out + s.TH - 1) / s.TH;
+        s.IH = (s.TH - 1) * s.strideH + (s.kH - 1) * s.dilH + 1;
+        const int IW = (s.TW - 1) * s.strideW + (s.kW - 1) * s.dilW + 1;
+        // the window starts at column bw*TW*strideW - padW; TW*strideW is a multiple of 8, so rounding
+        // the start down to a multiple of 8 elements (16 bytes) shifts every tile by the same xoff
+        s.xoff = ((-s.padW % 8) + 8) % 8;
+        s.IWp = (IW + s.xoff + 7) / 8 * 8;
+        s.in_off = ring_bytes + kMiscBytes;
+        const long long in_bytes = (long long)s.C_in * s.IH * s.IWp * 2;
+        const long long tiles = (long long)s.N * s.tiles_h * s.tiles_w;
+        if (s.IH <= 256 && s.IWp <= 256 && s.in_off + in_bytes <= kMaxSmem && in_bytes <= 112 * 1024 &&
+            tiles < (1ll << 31)) {
+            s.in_bytes = (int)in_bytes;
+            const uint64_t dims[4] = {(uint64_t)s.W, (uint64_t)s.H, (uint64_t)s.C_in, (uint64_t)s.N};
+            const uint64_t str[3] = {(uint64_t)s.W * 2, (uint64_t)s.H * s.W * 2, (uint64_t)s.C_in * s.H * s.W * 2};
+            const uint32_t box[4] = {(uint32_t)s.IWp, (uint32_t)s.IH, (uint32_t)s.C_in, 1};
+            halo = make_tmap(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, input, dims, str, box,
+                             CU_TENSOR_MAP_SWIZZLE_NONE);
+        }
     }
-    int* status = status_word();
-    if (status == nullptr) return kLaunchFailed;
+    if (halo) {
+        dim3 grid((unsigned)(s.N * s.tiles_h * s.tiles_w), (unsigned)n_blocks);
+        return launch_kernel<MODE, T, (T > 0)>(s, tm_b, tm_in, s.in_off + s.in_bytes, grid, input, weight, w_scale, bias,
+                                               output, stream);
+    }
+    s.in_off = 0;
+    s.in_bytes = 0;
     const long long tiles = (s.rows + kRows - 1) / kRows;
     if (tiles >= (1ll << 31)) return kTooLarge;
     dim3 grid((unsigned)tiles, (unsigned)n_blocks);
-    kern<<<grid, kThreads, smem, stream>>>(tm_b, s, input, weight, w_scale, bias, output, status);
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    return launch_kernel<MODE, T, false>(s, tm_b, tm_in, ring_bytes + kMiscBytes, grid, input, weight, w_scale, bias,
+                                         output, stream);
 }
 
 }  // namespace
@@ -404,7 +607,12 @@ int int8_conv2d_forward(const __half* input, const int8_t* weight, const __half*
     s.H_out = conv_out_size(H, padH, dilH, kH, strideH);
     s.W_out = conv_out_size(W, padW, dilW, kW, strideW);
     s.K = C_in * kH * kW;
-    return launch_conv<0>(s, input, weight, w_scale, bias, output, stream);
+    switch (kH * kW) {
+    case 1: return launch_conv<0, 1>(s, input, weight, w_scale, bias, output, stream);
+    case 4: return launch_conv<0, 4>(s, input, weight, w_scale, bias, output, stream);
+    case 9: return launch_conv<0, 9>(s, input, weight, w_scale, bias, output, stream);
+    default: return launch_conv<0, 0>(s, input, weight, w_scale, bias, output, stream);
+    }
 }
 
 int int8_conv_transpose2d_k2s2_forward(const __half* input, const int8_t* weight, const __half* w_scale,
@@ -418,7 +626,7 @@ int int8_conv_transpose2d_k2s2_forward(const __half* input, const int8_t* weight
     s.kH = 1; s.kW = 1; s.padH = 0; s.padW = 0; s.strideH = 1; s.strideW = 1; s.dilH = 1; s.dilW = 1;
     s.H_out = H; s.W_out = W;
     s.K = C_in;
-    return launch_conv<1>(s, input, weight, w_scale, bias, output, stream);
+    return launch_conv<1, 1>(s, input, weight, w_scale, bias, output, stream);
 }
 
 }  // namespace fb200

@@ -100,6 +100,19 @@ def test_conv2d_reference_cases(C_in, H, W, C_out, k, p, s, d, use_bias):
     (1, 128, 12, 12, 48, (3, 3), (0, 0), (1, 1), (1, 1), True),     # K = 1152, no padding
     (4, 16, 7, 7, 16, (7, 7), (3, 3), (1, 1), (1, 1), True),        # kernel as large as the image
     (1, 1, 1, 1, 1, (1, 1), (0, 0), (1, 1), (1, 1), True),          # one position, one tap
+    (2, 19, 21, 23, 16, (3, 3), (1, 1), (2, 2), (1, 1), True),      # C_in % 4 = 3: leftover-channel path, stride 2
+    (2, 6, 30, 30, 16, (2, 2), (0, 0), (2, 2), (1, 1), False),      # 2x2 taps, C_in % 4 = 2
+    (1, 130, 9, 9, 40, (1, 1), (0, 0), (1, 1), (1, 1), True),       # pointwise, K = 130: a 2-tap second stage
+    (1, 57, 16, 16, 32, (3, 3), (1, 1), (1, 1), (1, 1), True),      # K = 513: a 1-tap fifth stage
+    # image widths that are multiples of 8 take the input-window (TMA) variant
+    (3, 16, 21, 40, 32, (3, 3), (1, 1), (1, 1), (1, 1), True),      # ragged block rows, three samples
+    (2, 12, 30, 48, 16, (3, 3), (2, 2), (1, 1), (2, 2), True),      # dilation 2, pad 2: window starts 2 columns left
+    (2, 8, 33, 64, 24, (3, 3), (1, 1), (2, 2), (1, 1), False),      # stride 2
+    (1, 128, 20, 24, 64, (3, 3), (1, 1), (1, 1), (1, 1), True),     # 128 channels: a 73 KB window, W_out < 32
+    (1, 32, 9, 8, 16, (3, 3), (3, 3), (1, 1), (1, 1), True),        # pad 3 > kernel reach, 8-wide blocks
+    (2, 20, 64, 72, 48, (1, 1), (0, 0), (1, 1), (1, 1), True),      # pointwise through the window variant
+    (1, 16, 24, 32, 16, (2, 2), (0, 0), (2, 2), (1, 1), True),      # 2x2 stride 2
+    (1, 16, 16, 16, 16, (3, 3), (9, 9), (1, 1), (1, 1), True),      # pad 9: xoff = 7, blocks fully outside the image
 ])
 def test_conv2d_batches_and_shapes(N, C_in, H, W, C_out, k, p, s, d, use_bias):
     _check_conv(N, C_in, H, W, C_out, k, p, s, d, use_bias, seed=7 + C_in + C_out)
@@ -124,6 +137,29 @@ def test_conv2d_zero_image_and_outliers():
     assert np.array_equal(out.cpu().numpy().view(np.uint16), expect.view(np.uint16))
     # a zero image gives exactly the bias
     assert torch.equal(out[0].cpu(), bias.view(C_out, 1, 1).expand(C_out, H, W))
+
+
+def test_conv2d_non_finite_pixels_follow_the_quantizer():
+    """Infinities and NaNs go through the same value step as the standalone quantizer (saturate, NaN -> 0):
+    checked against the composed pipeline, which runs that quantizer."""
+    N, C_in, H, W, C_out = 1, 8, 12, 12, 16
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn((N, C_in, H, W), generator=g).to(torch.float16)
+    x[0, 1, 2, 2] = float("inf")
+    x[0, 2, 8, 8] = float("-inf")
+    x[0, 5, 5, 10] = float("nan")
+    w = torch.randint(-127, 128, (C_out, C_in * 9), generator=g, dtype=torch.int8)
+    w_scale, bias = _scales(C_out, True, g)
+    out = C.int8_conv2d_forward(x.to(DEV), w.to(DEV), w_scale.to(DEV), bias.to(DEV), (3, 3), (1, 1))
+    expect = _composed_conv(x, w, w_scale, bias, (3, 3), (1, 1), (1, 1), (1, 1))
+    got = out.cpu().numpy()
+    # NaN outputs (0 * inf scale) carry different payloads on the CPU and the GPU; everything else bit-exact
+    both_nan = np.isnan(got) & np.isnan(expect)
+    assert both_nan.any() and not both_nan.all()
+    assert np.array_equal(got.view(np.uint16)[~both_nan], expect.view(np.uint16)[~both_nan])
+    if O.ref_available():
+        ref = O.ref_int8_conv2d(x.to(DEV), w.to(DEV), w_scale.to(DEV), bias.to(DEV), 3, 3, 1, 1, 1, 1, 1, 1)
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
 
 
 def test_conv2d_output_fully_overwritten_and_repeatable():

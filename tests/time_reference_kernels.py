@@ -142,6 +142,36 @@ def main():
     t_new = timed(lambda: C.pack_metadata(raw, packed, N, K), args.iters, flush)
     report("pack_metadata", f"N={N} K={K}", "GB/s", 0.375 * N * K / 1e6, t_ref, t_new, same_pack)
 
+    # INT8 conv callers (the reference runs im2col / quantize / GEMM / transpose per sample).
+    for (N, Ci, H, W, Co) in [(1, 16, 540, 960, 32), (1, 16, 1080, 1920, 32), (4, 64, 128, 128, 64)]:
+        g = torch.Generator(device=DEV).manual_seed(12)
+        x = torch.randn((N, Ci, H, W), device=DEV, generator=g).half()
+        wq = rand_i8((Co, Ci * 9), 13)
+        _, w, b = scales(1, Co, 4)
+        o_ref = ol.ref_int8_conv2d(x, wq, w, b, 3, 3, 1, 1, 1, 1, 1, 1)
+        o_new = C.int8_conv2d_forward(x, wq, w, b, (3, 3), (1, 1))
+        ws = torch.empty(int(ol.ref().ref_int8_conv2d_workspace_size(Ci, H, W, Co, 3, 3, 1, 1, 1, 1, 1, 1)) + 16,
+                         dtype=torch.uint8, device=DEV)
+        st = ol.cur_stream()
+        t_ref = timed(lambda: ol.ref().ref_int8_conv2d_forward(ol.tp(x), ol.tp(wq), ol.tp(w), ol.tp(b), ol.tp(o_ref), N,
+                                                               Ci, H, W, Co, 3, 3, 1, 1, 1, 1, 1, 1, ol.tp(ws), st),
+                      args.iters, flush)
+        t_new = timed(lambda: C.int8_conv2d_forward(x, wq, w, b, (3, 3), (1, 1)), args.iters, flush)
+        report("int8_conv2d_forward 3x3", f"N={N} C_in={Ci} {H}x{W} C_out={Co}", "GB/s (input + output bytes)",
+               (2.0 * x.numel() + 2.0 * o_new.numel() + wq.numel()) / 1e6, t_ref, t_new, torch.equal(o_ref, o_new))
+        wt = rand_i8((4 * Co, Ci), 14)
+        o_ref = ol.ref_int8_conv_transpose2d_k2s2(x, wt, w, b)
+        o_new = C.int8_conv_transpose2d_k2s2_forward(x, wt, w, b)
+        ws = torch.empty(int(ol.ref().ref_int8_conv_transpose2d_k2s2_workspace_size(Ci, H, W, Co)) + 16,
+                         dtype=torch.uint8, device=DEV)
+        t_ref = timed(lambda: ol.ref().ref_int8_conv_transpose2d_k2s2_forward(ol.tp(x), ol.tp(wt), ol.tp(w), ol.tp(b),
+                                                                              ol.tp(o_ref), N, Ci, H, W, Co, ol.tp(ws),
+                                                                              st), args.iters, flush)
+        t_new = timed(lambda: C.int8_conv_transpose2d_k2s2_forward(x, wt, w, b), args.iters, flush)
+        report("int8_conv_transpose2d_k2s2", f"N={N} C_in={Ci} {H}x{W} C_out={Co}", "GB/s (input + output bytes)",
+               (2.0 * x.numel() + 2.0 * o_new.numel() + wt.numel()) / 1e6, t_ref, t_new, torch.equal(o_ref, o_new))
+        del x, o_ref, o_new, ws
+
     lines = ["| entry point | shape | reference kernel on B200 | this library | unit | speed-up | bit-identical |",
              "|---|---|---|---|---|---|---|"]
     for r in rows:
