@@ -400,11 +400,14 @@ def run_case(args):
             w_s = (torch.rand(co, generator=g, device=dev) * 0.02 + 0.001).half()
             bias = (torch.randn(co, generator=g, device=dev) * 0.01).half()
             if name == "conv":
-                wq = ri8(co, ci * 9)
-                out = torch.empty((nb, co, hh, ww), dtype=torch.float16, device=dev)
+                ks = args.ksize            # 3: 3x3 pad 1; 1: pointwise; 2: 2x2 stride 2
+                pad, st = (1, 1) if ks == 3 else (0, 1) if ks == 1 else (0, 2)
+                ho, wo = (hh + 2 * pad - ks) // st + 1, (ww + 2 * pad - ks) // st + 1
+                wq = ri8(co, ci * ks * ks)
+                out = torch.empty((nb, co, ho, wo), dtype=torch.float16, device=dev)
                 fn = lambda: lib.forge_int8_conv2d_forward(x.data_ptr(), wq.data_ptr(), w_s.data_ptr(), bias.data_ptr(),
-                                                           out.data_ptr(), nb, ci, hh, ww, co, 3, 3, 1, 1, 1, 1, 1, 1, 0,
-                                                           S[0])
+                                                           out.data_ptr(), nb, ci, hh, ww, co, ks, ks, pad, pad, st, st,
+                                                           1, 1, 0, S[0])
             else:
                 wq = ri8(4 * co, ci)
                 out = torch.empty((nb, co, 2 * hh, 2 * ww), dtype=torch.float16, device=dev)
@@ -413,7 +416,7 @@ def run_case(args):
                                                                           ww, co, 0, S[0])
             # minimum traffic: the input and the weight read once, the output written once
             work, unit, bound = (2.0 * x.numel() + wq.numel() + 2.0 * out.numel()) / 1e9, "GB/s", "hbm"
-            shape = {"N": nb, "C_in": ci, "H": hh, "W": ww, "C_out": co}
+            shape = {"N": nb, "C_in": ci, "H": hh, "W": ww, "C_out": co, "kernel": args.ksize if name == "conv" else 2}
         elif name in ("mlp", "mlp_sparse"):
             # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
             m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
@@ -589,6 +592,8 @@ def main():
     ap.add_argument("--reps", type=int, default=1,
                     help="--case runs: back-to-back calls per timed region (hides host launch latency of "
                          "microsecond-sized kernels; inputs then stay in L2 after the first call)")
+    ap.add_argument("--ksize", type=int, default=3, choices=[1, 2, 3],
+                    help="conv case: 3 = 3x3 pad 1, 1 = pointwise, 2 = 2x2 stride 2")
     ap.add_argument("--height", type=int, default=1080, help="conv cases: input height")
     ap.add_argument("--width", type=int, default=1920, help="conv cases: input width")
     ap.add_argument("--rotate", type=int, default=1,

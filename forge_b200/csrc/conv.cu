@@ -58,6 +58,8 @@ struct ConvShape {
     int in_off, in_bytes;     // window's place in shared memory
 };
 
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 __device__ __forceinline__ uint32_t pack4(int q0, int q1, int q2, int q3) {
     return (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
            ((uint32_t)(q3 & 0xFF) << 24);
@@ -66,6 +68,15 @@ __device__ __forceinline__ uint32_t pack4(int q0, int q1, int q2, int q3) {
 // The quantizer's value step; the byte in the low 8 bits.
 __device__ __forceinline__ uint32_t quant_byte(float x, float inv_scale) {
     return static_cast<uint32_t>(quant_value(x, inv_scale)) & 0xFFu;
+}
+
+// Four s32 values -> four saturated s8 bytes (first value in the low byte): the quantizer's clamp
+// to [-128, 127] and the byte packing in two instructions.
+__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(q1), "r"(q0), "r"(hi));
+    return d;
 }
 
 // Walks the taps of one patch in (c, kh, kw) order.
@@ -134,7 +145,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
     const int num_kb = (s.K + 127) / 128;
     const bool has_bias = (bias != nullptr);
 
-    if (threadIdx.x == 0) {
+    // The loader thread sets up the barriers and starts the window and the first weight tiles at once,
+    // so their latency overlaps the TMEM allocation and the rest of the prologue.
+    const int b_prefetched = s.b_by_tma ? min(s.stages, num_kb) : 0;
+    if (warp_id == 4 && lane == 0) {
         for (int i = 0; i < kStages; i++) {
             mbar_init(&full_bar[i], 5);
             mbar_init(&empty_bar[i], 1);
@@ -143,20 +157,33 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
         mbar_init(in_full, 1);
         *abort_flag = 0;
         fence_mbar_init();
-    }
-    if (warp_id == 4 && lane == 0) {
-        if (s.b_by_tma) prefetch_tensormap(&tm_b);
-        if (HALO) prefetch_tensormap(&tm_in);
+        if (HALO) {
+            mbar_expect_tx(in_full, s.in_bytes);
+            tma_load_4d(smem + s.in_off, &tm_in, in_full, t_bw * s.TW * s.strideW - s.padW - s.xoff,
+                        t_bh * s.TH * s.strideH - s.padH, 0, t_smp);
+        }
+        for (int kb = 0; kb < b_prefetched; kb++) {
+            mbar_expect_tx(&full_bar[kb], s.ct * 128);
+            tma_load_2d(smem + kb * stage_bytes + kABytes, &tm_b, &full_bar[kb], kb * 128, n0);
+        }
     }
     if (warp_id == 5) {
         tmem_alloc(tmem_base_slot, s.tmem_cols);
         tmem_relinquish();
     }
-    for (int i = threadIdx.x; i < s.ct; i += kThreads) {
-        const int n = n0 + i;
-        const int co = (MODE == 1) ? (n >> 2) : n;
-        s_ws[i] = (n < s.cols) ? __half2float(w_scale[co]) : 0.f;
-        s_bias[i] = (has_bias && n < s.cols) ? __half2float(bias[co]) : 0.f;
+    // weight scales and bias of this CTA's columns: loaded now, parked in shared memory before the epilogue
+    float r_ws[2] = {0.f, 0.f}, r_bias[2] = {0.f, 0.f};
+    if (warp_id < 4) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = threadIdx.x + u * kRows;
+            const int n = n0 + i;
+            if (i < s.ct && n < s.cols) {
+                const int co = (MODE == 1) ? (n >> 2) : n;
+                r_ws[u] = __half2float(__ldg(w_scale + co));
+                if (has_bias) r_bias[u] = __half2float(__ldg(bias + co));
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -228,7 +255,25 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
                 return ((inside >> j) & 1u) ? __half2float(__ldg(p + off[j])) : 0.f;
             };
             float amax = 0.f;
-            if (ok) {
+            if (HALO) {
+                // |x| maximum over the channels of every window pixel, two pixels per thread and step,
+                // then the maximum over this position's T pixels. (Runs even after a failed wait so
+                // that all four warps meet at the barrier; the result is then unused.)
+                __half2* pmap = reinterpret_cast<__half2*>(smem + s.in_off + s.in_bytes);
+                const __half2* win2 = reinterpret_cast<const __half2*>(in_tile);
+                const int pairs = (s.IH * s.IWp) >> 1;
+                for (int idx = threadIdx.x; idx < pairs; idx += kRows) {
+                    __half2 mx = __float2half2_rn(0.f);
+                    const __half2* pw = win2 + idx;
+#pragma unroll 8
+                    for (int c = 0; c < s.C_in; c++, pw += pairs) mx = __hmax2(mx, __habs2(*pw));
+                    pmap[idx] = mx;
+                }
+                named_barrier_sync(1, kRows);
+                const __half* pm = reinterpret_cast<const __half*>(pmap);
+#pragma unroll
+                for (int j = 0; j < T; j++) amax = max_ftz(amax, __half2float(pm[off[j]]));
+            } else if (ok) {
                 const __half* pc = pc0;
 #pragma unroll G
                 for (int c = 0; c < s.C_in; c++, pc += plane) {
@@ -263,6 +308,46 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
             };
             const __half* pc = pc0;
             int c = 0;
+            if (HALO) {
+                // GC channels = GC*T taps = whole 16-byte chunks of the patch row
+                constexpr int GC = (T == 4) ? 4 : 16;
+                constexpr int TT = (T > 0) ? T : 1;
+                const int plane_i = s.IH * s.IWp;
+                for (; c + GC <= s.C_in; c += GC, pc += GC * plane) {
+#pragma unroll
+                    for (int ch = 0; ch < GC * T / 16; ch++) {
+                        int q[16];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const int tp = ch * 16 + i;     // tap within the group: channel tp / T, pixel tp % T
+                            q[i] = cvt_rni_ftz(mul_ftz(__half2float(pc[(tp / TT) * plane_i + off[tp % TT]]), inv));
+                        }
+                        if (ok) {
+                            if ((wi & 31) == 0) {
+                                const int kb = wi >> 5;
+                                const int stage = kb % s.stages;
+                                if (!__all_sync(0xffffffffu,
+                                                mbar_wait(&empty_bar[stage], ((kb / s.stages) & 1) ^ 1, abort_flag))) {
+                                    atomicExch(status, 601);
+                                    ok = false;
+                                }
+                                rowp = smem + stage * stage_bytes + r * 128;
+                            }
+                        }
+                        if (ok) {
+                            *reinterpret_cast<uint4*>(rowp + ((((wi >> 2) & 7) ^ (r & 7)) << 4)) =
+                                make_uint4(pack4_sat(q[0], q[1], q[2], q[3]), pack4_sat(q[4], q[5], q[6], q[7]),
+                                           pack4_sat(q[8], q[9], q[10], q[11]), pack4_sat(q[12], q[13], q[14], q[15]));
+                            if ((wi & 31) == 28) {
+                                fence_proxy_async_smem();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&full_bar[(wi >> 5) % s.stages]);
+                            }
+                            wi += 4;
+                        }
+                    }
+                }
+            }
             for (; c + G <= s.C_in; c += G, pc += G * plane) {
                 uint32_t q[G * (T > 0 ? T : 1)];
 #pragma unroll
@@ -343,6 +428,15 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
             }
         }
 
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = threadIdx.x + u * kRows;
+            if (i < s.ct) {
+                s_ws[i] = r_ws[u];
+                s_bias[i] = r_bias[u];
+            }
+        }
+        named_barrier_sync(1, kRows);
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tmem_full, 0, abort_flag));
         if (!ok) {
             atomicExch(status, 602);
@@ -392,13 +486,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
         }
     } else if (warp_id == 4) {
         // ------------------------------------------------------------ input window, weight tiles
-        if (HALO && lane == 0) {
-            mbar_expect_tx(in_full, s.in_bytes);
-            tma_load_4d(smem + s.in_off, &tm_in, in_full, t_bw * s.TW * s.strideW - s.padW - s.xoff,
-                        t_bh * s.TH * s.strideH - s.padH, 0, t_smp);
-        }
         bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; kb++) {
+        for (int kb = b_prefetched; kb < num_kb && ok; kb++) {
             const int stage = kb % s.stages;
             const uint32_t phase = (kb / s.stages) & 1;
             uint8_t* sb = smem + stage * stage_bytes + kABytes;
@@ -419,18 +508,28 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constan
                     ok = false;
                     break;
                 }
-                for (int idx = lane; idx < s.ct * 8; idx += 32) {
-                    const int row = idx >> 3, ch = idx & 7;
+                // only the 16-byte chunks the MMA steps of this slab read: 2 per 32-tap step
+                const int taps = min(128, s.K - kb * 128);
+                const int chunks = 2 * ((taps + 31) / 32);
+                const bool vec = (s.K % 16 == 0) && aligned16_dev(weight);
+                for (int idx = lane; idx < s.ct * chunks; idx += 32) {
+                    const int row = idx / chunks, ch = idx - row * chunks;
                     const int n = n0 + row;
                     const int k0 = kb * 128 + ch * 16;
-                    uint32_t p[4] = {0u, 0u, 0u, 0u};
-                    if (n < s.cols) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (n < s.cols && k0 < s.K) {
                         const int8_t* src = weight + (size_t)n * s.K + k0;
+                        if (vec) {
+                            v = __ldg(reinterpret_cast<const uint4*>(src));
+                        } else {
+                            uint32_t p[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (k0 + j < s.K) p[j >> 2] |= (uint32_t)(uint8_t)src[j] << (8 * (j & 3));
+                            for (int j = 0; j < 16; j++)
+                                if (k0 + j < s.K) p[j >> 2] |= (uint32_t)(uint8_t)__ldg(src + j) << (8 * (j & 3));
+                            v = make_uint4(p[0], p[1], p[2], p[3]);
+                        }
                     }
-                    *reinterpret_cast<uint4*>(sb + row * 128 + ((ch ^ (row & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+                    *reinterpret_cast<uint4*>(sb + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -502,6 +601,12 @@ int launch_kernel(const ConvShape& s, const CUtensorMap& tm_b, const CUtensorMap
     }
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
+    // Never let more CTAs become resident on an SM than its 512 TMEM columns serve: a CTA that has to
+    // wait inside tcgen05.alloc for another one's columns was measured to cost far more than the lost
+    // occupancy. Shared memory is the lever: ask for enough that one CTA more would not fit.
+    const int by_tmem = 512 / s.tmem_cols;
+    const int floor_smem = (228 * 1024) / (by_tmem + 1) - 1024 + 16;
+    smem = std::min(std::max(smem, floor_smem), kMaxSmem);
     kern<<<grid, kThreads, smem, stream>>>(tm_b, tm_in, s, input, weight, w_scale, bias, output, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
@@ -521,7 +626,9 @@ int launch_conv(ConvShape s, const __half* input, const int8_t* weight, const __
     s.ct = (((s.cols + n_blocks - 1) / n_blocks) + 15) / 16 * 16;
     s.tmem_cols = 32;
     while (s.tmem_cols < s.ct) s.tmem_cols *= 2;
-    s.b_by_tma = (s.K % 16 == 0 && aligned16(weight)) ? 1 : 0;
+    // TMA for the weight tiles only when every row starts on a 32-byte sector: with 16- or 48-byte rows
+    // the per-row requests of a 128-row box were measured to take microseconds per tile
+    s.b_by_tma = (s.K % 32 == 0 && aligned16(weight)) ? 1 : 0;
     s.stages = std::min(kStages, (s.K + 127) / 128);
     const int ring_bytes = s.stages * (kABytes + s.ct * 128);
 
@@ -553,7 +660,8 @@ int launch_conv(ConvShape s, const __half* input, const int8_t* weight, const __
         s.in_off = ring_bytes + kMiscBytes;
         const long long in_bytes = (long long)s.C_in * s.IH * s.IWp * 2;
         const long long tiles = (long long)s.N * s.tiles_h * s.tiles_w;
-        if (s.IH <= 256 && s.IWp <= 256 && s.in_off + in_bytes <= kMaxSmem && in_bytes <= 112 * 1024 &&
+        const long long pmap_bytes = (long long)s.IH * s.IWp * 2;   // per-pixel channel absmax of the window
+        if (s.IH <= 256 && s.IWp <= 256 && s.in_off + in_bytes + pmap_bytes <= kMaxSmem && in_bytes <= 112 * 1024 &&
             tiles < (1ll << 31)) {
             s.in_bytes = (int)in_bytes;
             const uint64_t dims[4] = {(uint64_t)s.W, (uint64_t)s.H, (uint64_t)s.C_in, (uint64_t)s.N};
@@ -565,8 +673,8 @@ int launch_conv(ConvShape s, const __half* input, const int8_t* weight, const __
     }
     if (halo) {
         dim3 grid((unsigned)(s.N * s.tiles_h * s.tiles_w), (unsigned)n_blocks);
-        return launch_kernel<MODE, T, (T > 0)>(s, tm_b, tm_in, s.in_off + s.in_bytes, grid, input, weight, w_scale, bias,
-                                               output, stream);
+        return launch_kernel<MODE, T, (T > 0)>(s, tm_b, tm_in, s.in_off + s.in_bytes + s.IH * s.IWp * 2, grid, input,
+                                               weight, w_scale, bias, output, stream);
     }
     s.in_off = 0;
     s.in_bytes = 0;

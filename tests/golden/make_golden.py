@@ -1,8 +1,9 @@
-"""Generates tests/golden/reference_vectors.npz: small seeded inputs together with the outputs
-of the REFERENCE's own CUDA kernels (oracle/_ref/libforge_ref.so, built from the reference
-sources for sm_100a by oracle/build.py). Needs a GPU:
+"""Generates tests/golden/reference_vectors.npz and tests/golden/reference_conv_vectors.npz: small
+seeded inputs together with the outputs of the REFERENCE's own CUDA kernels
+(oracle/_ref/libforge_ref.so, built from the reference sources for sm_100a by oracle/build.py).
+Needs a GPU:
 
-    python tests/golden/make_golden.py [output.npz]
+    python tests/golden/make_golden.py [output.npz [conv_output.npz]]
 
 The committed .npz pins the CPU oracle in the CPU-only test run (tests/test_oracle_cpu.py).
 """
@@ -80,5 +81,55 @@ def main(out_path):
     print("wrote", out_path, {k: v.shape for k, v in out.items()})
 
 
+def conv_vectors(out_path):
+    """The reference's conv pipelines on its own test shapes (tests/test_int8_conv2d.cu:206-257,
+    tests/test_int8_special_conv.cu:282-284), one sample each. Besides the output, the int8 patches and
+    their scales are read back from the reference's workspace ([fp16 col | int8 col | fp32 scales | ...],
+    src/nn/int8_conv2d.cu:172-176), which pins every later step on the CPU exactly."""
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(20240602)
+    out = {}
+    cases = {"c0": (8, 16, 16, 16, 3, 3, 1, 1, 1, 1, 1, 1, True), "c1": (7, 32, 32, 16, 2, 2, 0, 0, 2, 2, 1, 1, True),
+             "c2": (4, 12, 12, 8, 3, 3, 1, 1, 1, 1, 1, 1, False), "c3": (8, 16, 16, 8, 3, 3, 2, 2, 1, 1, 2, 2, True)}
+    for name, (Ci, H, W, Co, kH, kW, pH, pW, sH, sW, dH, dW, use_bias) in cases.items():
+        K = Ci * kH * kW
+        x = (torch.rand((1, Ci, H, W), generator=g) * 2 - 1).to(torch.float16)
+        w = torch.randint(-127, 128, (Co, K), generator=g, dtype=torch.int8)
+        w_s = (torch.rand(Co, generator=g) * 0.045 + 0.005).to(torch.float16)
+        bias = (torch.rand(Co, generator=g) - 0.5).to(torch.float16) if use_bias else None
+        Ho, Wo = O.conv_out_size(H, pH, dH, kH, sH), O.conv_out_size(W, pW, dW, kW, sW)
+        M = Ho * Wo
+        ws = torch.zeros(int(O.ref().ref_int8_conv2d_workspace_size(Ci, H, W, Co, kH, kW, pH, pW, sH, sW, dH, dW)) + 16,
+                         dtype=torch.uint8, device=dev)
+        y = torch.empty((1, Co, Ho, Wo), dtype=torch.float16, device=dev)
+        xd, wd, sd = x.to(dev), w.to(dev), w_s.to(dev)
+        bd = None if bias is None else bias.to(dev)
+        O.ref().ref_int8_conv2d_forward(O.tp(xd), O.tp(wd), O.tp(sd), O.tp(bd), O.tp(y), 1, Ci, H, W, Co, kH, kW, pH, pW,
+                                        sH, sW, dH, dW, O.tp(ws), O.cur_stream())
+        torch.cuda.synchronize()
+        wsb = ws.cpu().numpy()
+        out[name + "_cfg"] = np.array([Ci, H, W, Co, kH, kW, pH, pW, sH, sW, dH, dW], np.int32)
+        out[name + "_x"], out[name + "_w"], out[name + "_ws"] = x.numpy(), w.numpy(), w_s.numpy()
+        if bias is not None:
+            out[name + "_bias"] = bias.numpy()
+        out[name + "_q"] = wsb[2 * M * K:3 * M * K].view(np.int8).reshape(M, K).copy()
+        out[name + "_as"] = wsb[3 * M * K:3 * M * K + 4 * M].view(np.float32).copy()
+        out[name + "_y"] = y.cpu().numpy()
+    # 2x2 stride-2 transposed conv
+    for name, (Ci, H, W, Co, use_bias) in {"t0": (32, 16, 16, 64, True), "t1": (16, 32, 32, 16, False)}.items():
+        x = (torch.rand((1, Ci, H, W), generator=g) * 2 - 1).to(torch.float16)
+        w = torch.randint(-127, 128, (4 * Co, Ci), generator=g, dtype=torch.int8)
+        w_s = (torch.rand(Co, generator=g) * 0.045 + 0.005).to(torch.float16)
+        bias = (torch.rand(Co, generator=g) - 0.5).to(torch.float16) if use_bias else None
+        y = O.ref_int8_conv_transpose2d_k2s2(x.to(dev), w.to(dev), w_s.to(dev), None if bias is None else bias.to(dev))
+        out[name + "_x"], out[name + "_w"], out[name + "_ws"] = x.numpy(), w.numpy(), w_s.numpy()
+        if bias is not None:
+            out[name + "_bias"] = bias.numpy()
+        out[name + "_y"] = y.cpu().numpy()
+    np.savez_compressed(out_path, **out)
+    print("wrote", out_path, {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "reference_vectors.npz"))
+    conv_vectors(sys.argv[2] if len(sys.argv) > 2 else os.path.join(HERE, "reference_conv_vectors.npz"))
