@@ -83,3 +83,56 @@ def test_fp16_conversion_matches_numpy():
         want = int(np.float32(v).astype(np.float16).view(np.uint16)) if abs(v) < 65520 else None
         if want is not None:
             assert lib.oracle_float_to_half(float(v)) == want
+
+
+# ---------------------------------------------------------------- INT8 conv callers
+CONV_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_conv_vectors.npz")
+
+
+@pytest.fixture(scope="module")
+def conv_gold():
+    return np.load(CONV_GOLDEN)
+
+
+@pytest.mark.parametrize("case", ["c0", "c1", "c2", "c3"])
+def test_conv2d_chain_against_reference_pipeline(conv_gold, case):
+    """The reference's conv pipeline ran on a B200; its int8 patches and scales were read back from
+    its workspace. From those, the oracle's exact steps (s32 GEMM, GEMM-epilogue dequant + bias,
+    transpose) must reproduce the reference output bit for bit; the oracle's im2col + IEEE quantizer
+    must land within one int8 step of the reference's patches, and the end-to-end CPU conv within
+    the output change one step can cause."""
+    g = conv_gold
+    Ci, H, W, Co, kH, kW, pH, pW, sH, sW, dH, dW = [int(v) for v in g[case + "_cfg"]]
+    x, w, w_s, q_ref, a_ref, y_ref = (g[case + k] for k in ("_x", "_w", "_ws", "_q", "_as", "_y"))
+    bias = g[case + "_bias"] if case + "_bias" in g.files else None
+    col, Ho, Wo = O.im2col(x, kH, kW, pH, pW, sH, sW, dH, dW)
+    assert col.shape == q_ref.shape
+    acc = O.gemm_s32(q_ref, w)
+    y = O.rows_to_nchw(O.dequantize_bias(acc, a_ref, w_s, bias, gemm_epilogue=True), 1, Ho * Wo, Co)
+    assert np.array_equal(y.reshape(y_ref.shape).view(np.uint16), y_ref.view(np.uint16))
+    q, a = O.quantize(col)
+    assert np.abs(q.astype(np.int32) - q_ref.astype(np.int32)).max() <= 1
+    np.testing.assert_allclose(a, a_ref, rtol=1e-6)
+    y_cpu = O.int8_conv2d(x, w, w_s, bias, kH, kW, pH, pW, sH, sW, dH, dW).astype(np.float32)
+    # one int8 step on every tap moves an output by at most scale * w_scale * sum|w|
+    bound = (a_ref.max() * w_s.astype(np.float32) * np.abs(w.astype(np.float32)).sum(axis=1)).reshape(1, Co, 1, 1)
+    assert (np.abs(y_cpu - y_ref.astype(np.float32)) <= bound + 1e-2).all()
+    assert np.mean(y_cpu.astype(np.float16).view(np.uint16) == y_ref.view(np.uint16)) > 0.9
+
+
+@pytest.mark.parametrize("case,H,W", [("t0", 16, 16), ("t1", 32, 32)])
+def test_conv_transpose_chain_against_reference_pipeline(conv_gold, case, H, W):
+    g = conv_gold
+    x, w, w_s, y_ref = (g[case + k] for k in ("_x", "_w", "_ws", "_y"))
+    bias = g[case + "_bias"] if case + "_bias" in g.files else None
+    Co = w.shape[0] // 4
+    col, _, _ = O.im2col(x, 1, 1, 0, 0, 1, 1, 1, 1)
+    q, a = O.quantize(col)
+    acc = O.gemm_s32(q, w)
+    gem = O.dequantize_bias(acc, a, np.repeat(w_s, 4), None, gemm_epilogue=True)
+    y = O.conv_transpose_k2s2_scatter(gem, bias, 1, H, W, Co)
+    # the CPU quantizer may differ from the GPU's by one int8 step on a few taps
+    same = np.mean(y.view(np.uint16) == y_ref.view(np.uint16))
+    assert same > 0.9, same
+    bound = (a.max() * w_s.astype(np.float32) * np.abs(w.astype(np.float32)).reshape(Co, -1).sum(axis=1) / 4)
+    assert (np.abs(y.astype(np.float32) - y_ref.astype(np.float32)) <= bound.reshape(1, Co, 1, 1) + 1e-2).all()
