@@ -86,48 +86,69 @@ namespace fb200 {
 
 namespace {
 
-// 32 weight bytes (8 groups) per thread -> 16 compressed bytes + 8 nibble bytes.
-// Valid when K % 4 == 0 (groups tile the flat array) and N*K % 32 == 0.
+// 16 weight bytes (4 groups) per piece -> 8 compressed bytes + 4 nibble bytes; a thread takes four
+// pieces 256 apart, so every load and store of a warp is one contiguous run (512 / 256 / 128 bytes)
+// and four loads are in flight per thread. Valid when K % 4 == 0 (groups tile the flat array) and
+// N*K % 16 == 0.
 __global__ void __launch_bounds__(256)
-prune_compress_vec_kernel(const uint4* __restrict__ weight, uint4* __restrict__ compressed,
-                          uint2* __restrict__ metadata_raw, long long nthreads) {
-    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (id >= nthreads) return;
-    const uint4 w0 = __ldcs(weight + 2 * id), w1 = __ldcs(weight + 2 * id + 1);
-    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    uint32_t comp[4] = {0u, 0u, 0u, 0u};
-    uint32_t meta[2] = {0u, 0u};
+prune_compress_vec_kernel(const uint4* __restrict__ weight, uint2* __restrict__ compressed,
+                          uint32_t* __restrict__ metadata_raw, long long npieces) {
+    const long long first = (long long)blockIdx.x * 1024 + threadIdx.x;
+    uint4 w[4];
 #pragma unroll
-    for (int g = 0; g < 8; g++) {
-        uint32_t kept;
-        const uint32_t nib = prune_group(w[g], kept);
-        comp[g >> 1] |= kept << (16 * (g & 1));
-        meta[g >> 2] |= nib << (8 * (g & 3));
+    for (int u = 0; u < 4; u++) {
+        const long long p = first + u * 256;
+        w[u] = (p < npieces) ? __ldcs(weight + p) : make_uint4(0u, 0u, 0u, 0u);
     }
-    compressed[id] = make_uint4(comp[0], comp[1], comp[2], comp[3]);
-    metadata_raw[id] = make_uint2(meta[0], meta[1]);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const long long p = first + u * 256;
+        if (p >= npieces) break;
+        const uint32_t g4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+        uint32_t comp[2] = {0u, 0u};
+        uint32_t meta = 0u;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            uint32_t kept;
+            const uint32_t nib = prune_group(g4[g], kept);
+            comp[g >> 1] |= kept << (16 * (g & 1));
+            meta |= nib << (8 * g);
+        }
+        __stcs(compressed + p, make_uint2(comp[0], comp[1]));
+        __stcs(metadata_raw + p, meta);
+    }
 }
 
-// 16 nibble bytes per thread -> two packed words. Valid when K % 32 == 0 and N*K/4 % 16 == 0.
+// 16 nibble bytes per piece -> two packed words; two pieces 256 apart per thread. Valid when
+// K % 32 == 0 and N*K/4 % 16 == 0.
 __global__ void __launch_bounds__(256)
-pack_metadata_vec_kernel(const uint4* __restrict__ meta_raw, uint2* __restrict__ meta_packed, long long nthreads) {
-    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (id >= nthreads) return;
-    const uint4 r = __ldcs(meta_raw + id);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-    uint32_t out[2];
+pack_metadata_vec_kernel(const uint4* __restrict__ meta_raw, uint2* __restrict__ meta_packed, long long npieces) {
+    const long long first = (long long)blockIdx.x * 512 + threadIdx.x;
+    uint4 r[2];
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        uint32_t p = 0;
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const uint32_t x = w[2 * h + j] & 0x0F0F0F0Fu;   // four nibbles, one per byte
-            const uint32_t four = (x & 0xF) | ((x >> 4) & 0xF0) | ((x >> 8) & 0xF00) | ((x >> 12) & 0xF000);
-            p |= four << (16 * j);
-        }
-        out[h] = p;
+    for (int u = 0; u < 2; u++) {
+        const long long p = first + u * 256;
+        r[u] = (p < npieces) ? __ldcs(meta_raw + p) : make_uint4(0u, 0u, 0u, 0u);
     }
-    meta_packed[id] = make_uint2(out[0], out[1]);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const long long p = first + u * 256;
+        if (p >= npieces) break;
+        const uint32_t w[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+        uint32_t out[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t pk = 0;
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const uint32_t x = w[2 * h + j] & 0x0F0F0F0Fu;   // four nibbles, one per byte
+                const uint32_t four = (x & 0xF) | ((x >> 4) & 0xF0) | ((x >> 8) & 0xF00) | ((x >> 12) & 0xF000);
+                pk |= four << (16 * j);
+            }
+            out[h] = pk;
+        }
+        __stcs(meta_packed + p, make_uint2(out[0], out[1]));
+    }
 }
 
 // One pass from a floating-point weight to everything a W8A8 layer stores: per-output-channel
@@ -198,13 +219,14 @@ int prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadat
     if (N <= 0 || K <= 0) return kOk;   // reference: silent no-op (prune_compress.cu:79)
     if (weight == nullptr || compressed == nullptr || metadata_raw == nullptr) return kBadPointer;
     const long long bytes = (long long)N * K;
-    const bool vec_ok = (K % 4 == 0) && (bytes % 32 == 0) && aligned16(weight) && aligned16(compressed) &&
-                        (reinterpret_cast<uintptr_t>(metadata_raw) % 8 == 0);
+    const bool vec_ok = (K % 4 == 0) && (bytes % 16 == 0) && aligned16(weight) &&
+                        (reinterpret_cast<uintptr_t>(compressed) % 8 == 0) &&
+                        (reinterpret_cast<uintptr_t>(metadata_raw) % 4 == 0);
     if (vec_ok) {
-        const long long n = bytes / 32;
-        prune_compress_vec_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-            reinterpret_cast<const uint4*>(weight), reinterpret_cast<uint4*>(compressed),
-            reinterpret_cast<uint2*>(metadata_raw), n);
+        const long long n = bytes / 16;
+        prune_compress_vec_kernel<<<(unsigned)((n + 1023) / 1024), 256, 0, stream>>>(
+            reinterpret_cast<const uint4*>(weight), reinterpret_cast<uint2*>(compressed),
+            reinterpret_cast<uint32_t*>(metadata_raw), n);
     } else {
         const long long groups = (long long)N * (K / 4);
         if (groups == 0) return kOk;
@@ -222,7 +244,7 @@ int pack_metadata(const uint8_t* meta_raw, uint32_t* meta_packed, int N, int K, 
                         (reinterpret_cast<uintptr_t>(meta_packed) % 8 == 0);
     if (vec_ok) {
         const long long n = nibbles / 16;
-        pack_metadata_vec_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+        pack_metadata_vec_kernel<<<(unsigned)((n + 511) / 512), 256, 0, stream>>>(
             reinterpret_cast<const uint4*>(meta_raw), reinterpret_cast<uint2*>(meta_packed), n);
     } else {
         const long long words = (long long)N * (K / 32);
