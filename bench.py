@@ -418,7 +418,7 @@ def run_case(args):
             work, unit, bound = (2.0 * x.numel() + wq.numel() + 2.0 * out.numel()) / 1e9, "GB/s", "hbm"
             shape = {"N": nb, "C_in": ci, "H": hh, "W": ww, "C_out": co, "kernel": args.ksize if name == "conv" else 2}
         elif name in ("mlp", "mlp_sparse"):
-            # BASELINE config 4: W8A8 gated MLP block, 8192 tokens, d_model 4096, d_ffn 14336
+            # W8A8 gated MLP block (Llama-style), default 8192 tokens, d_model 4096, d_ffn 14336
             m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
             x = torch.randn((m, dm), generator=g, device=dev, dtype=torch.float16)
 
@@ -505,7 +505,7 @@ def run_case(args):
 
 
 def run_sharded_case(args):
-    """BASELINE config 5: 2:4-sparse W8A8 linear, M tokens x K -> N, sharded over the ranks of a
+    """The sharded workload: 2:4-sparse W8A8 linear, M tokens x K -> N, sharded over the ranks of a
     torchrun launch. --case shard_rows: token rows split, no collective. --case shard_cols: output
     channels split, FP16 all-gather over NVLink. Prints one JSON line from rank 0 (device time,
     max over ranks)."""

@@ -2,8 +2,7 @@
 one exchange step that exists.
 
 The reference is single-GPU (no NCCL, MPI or peer access anywhere in its tree); this module is
-the additive layer BASELINE config 5 asks for. Two modes, both bit-identical to the single-GPU
-result because every output element is still one exact int32 accumulation followed by the same
+an additive layer. Two modes, both bit-identical to the single-GPU result because every output element is still one exact int32 accumulation followed by the same
 fp32 epilogue:
 
   rows     token rows are split across ranks, weights replicated. No communication at all: each

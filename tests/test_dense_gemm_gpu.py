@@ -15,7 +15,7 @@ from forge_b200 import _lib
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-# (M, K, N): tests/test_int8_dense_gemm.cu:13, tests/test_int8_dp4a_gemm.cu:181-199, BASELINE config 1,
+# (M, K, N): tests/test_int8_dense_gemm.cu:13, tests/test_int8_dp4a_gemm.cu:181-199, the 1024^3 benchmark shape,
 # ragged tiles, K tails that are not a multiple of the 128-byte slab, shapes off the TMA path.
 SHAPES = [(32, 128, 64), (1024, 1024, 1024), (37, 192, 208), (100, 640, 272), (129, 4096, 96), (2050, 512, 400),
           (1, 64, 16), (300, 1280, 384), (64, 256, 2112), (128, 16, 256), (257, 144, 520),

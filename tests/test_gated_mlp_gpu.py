@@ -1,4 +1,4 @@
-"""GPU parity of the gated-MLP path (BASELINE config 4: per-token quantize -> INT8 GEMM gate & up
+"""GPU parity of the gated-MLP path (W8A8 Llama-style MLP block: per-token quantize -> INT8 GEMM gate & up
 -> dequant + SiLU(gate)*up fused in the epilogue -> re-quantize -> INT8 GEMM down -> dequant),
 dense and 2:4-sparse, through the C ABI.
 

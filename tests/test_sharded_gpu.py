@@ -1,4 +1,4 @@
-"""Multi-GPU check of forge_b200/sharded.py (BASELINE config 5 at a reduced size): rows- and
+"""Multi-GPU check of forge_b200/sharded.py (the sharded 2:4-sparse W8A8 layer at a reduced size): rows- and
 columns-sharded 2:4-sparse W8A8 linear on 2 GPUs must equal the single-GPU result bit for bit.
 Spawns one process per GPU (NCCL over 127.0.0.1); skipped on single-GPU boxes."""
 import os

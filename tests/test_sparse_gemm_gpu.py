@@ -125,7 +125,7 @@ def test_every_nibble_in_every_group_position():
 
 @pytest.mark.parametrize("M", [1, 16, 128, 2048, 8192])
 def test_config3_shape_sampled(M):
-    """BASELINE config 3 (N=11008, K=4096): sparse result equals the dense GEMM on the pruned
+    """The Llama-MLP weight shape N=11008, K=4096 over the token sweep: sparse result equals the dense GEMM on the pruned
     weights, exact, on sampled tokens; repeat runs identical."""
     N, K = 11008, 4096
     g = torch.Generator(device=DEV).manual_seed(31)
