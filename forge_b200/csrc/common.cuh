@@ -113,6 +113,15 @@ __device__ __forceinline__ int quant_value(float x, float inv_scale) {
     return max(-128, min(127, q));
 }
 
+// Four s32 values -> four saturated s8 bytes (first value in the low byte): the quantizer's clamp
+// to [-128, 127] and the byte packing in two instructions.
+__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(q1), "r"(q0), "r"(hi));
+    return d;
+}
+
 // GEMM-epilogue dequantisation: (act_scale * w_scale) * acc (+ bias), one fp16 rounding.
 __device__ __forceinline__ float dequant_gemm(int acc, float as_ws, float bias, bool has_bias) {
     const float a = static_cast<float>(acc);

@@ -70,15 +70,6 @@ __device__ __forceinline__ uint32_t quant_byte(float x, float inv_scale) {
     return static_cast<uint32_t>(quant_value(x, inv_scale)) & 0xFFu;
 }
 
-// Four s32 values -> four saturated s8 bytes (first value in the low byte): the quantizer's clamp
-// to [-128, 127] and the byte packing in two instructions.
-__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
-    uint32_t hi, d;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(q1), "r"(q0), "r"(hi));
-    return d;
-}
-
 // Walks the taps of one patch in (c, kh, kw) order.
 struct TapWalker {
     int c, kh, kw;

@@ -87,22 +87,22 @@ quantize_rows_kernel(const __half* __restrict__ input, int8_t* __restrict__ outp
     uint2* out_row = reinterpret_cast<uint2*>(output + (size_t)(live ? row : 0) * K);
 
     uint4 v[VPT];
-    float tmax = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int idx = t + i * TPR;
         if (live && idx < nvec) v[i] = STREAM ? __ldcs(in_row + idx) : __ldg(in_row + idx);
         else v[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+    // |x| maximum in packed half precision: exact (no rounding in abs / max, NaNs are skipped like
+    // max.ftz.f32 skips them, fp16 subnormals are normal fp32 numbers so nothing is flushed)
+    __half2 hmax = __float2half2_rn(0.f);
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 f = __half22float2(h[j]);
-            tmax = max_ftz(tmax, max_ftz(abs_ftz(f.x), abs_ftz(f.y)));
-        }
+        for (int j = 0; j < 4; j++) hmax = __hmax2(hmax, __habs2(h[j]));
     }
+    float tmax = max_ftz(__low2float(hmax), __high2float(hmax));
     for (int off = 16; off > 0; off >>= 1) tmax = max_ftz(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
     if (WPR > 1) {
         __shared__ float part[BLOCK / 32];
@@ -123,15 +123,14 @@ quantize_rows_kernel(const __half* __restrict__ input, int8_t* __restrict__ outp
         const int idx = t + i * TPR;
         if (live && idx < nvec) {
             const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
-            uint32_t p[2] = {0u, 0u};
+            int q[8];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float2 f = __half22float2(h[j]);
-                const uint32_t q0 = (uint32_t)quant_value(f.x, inv) & 0xFFu;
-                const uint32_t q1 = (uint32_t)quant_value(f.y, inv) & 0xFFu;
-                p[j >> 1] |= (q0 << (16 * (j & 1))) | (q1 << (16 * (j & 1) + 8));
+                q[2 * j] = cvt_rni_ftz(mul_ftz(f.x, inv));          // the clamp to [-128, 127] is the pack's
+                q[2 * j + 1] = cvt_rni_ftz(mul_ftz(f.y, inv));
             }
-            out_row[idx] = make_uint2(p[0], p[1]);
+            out_row[idx] = make_uint2(pack4_sat(q[0], q[1], q[2], q[3]), pack4_sat(q[4], q[5], q[6], q[7]));
         }
     }
 }
