@@ -574,6 +574,81 @@ def run_sharded_case(args):
         dist.destroy_process_group()
 
 
+def run_sharded_mlp(args):
+    """W8A8 gated MLP block (8192 tokens per GPU, d_model 4096, d_ffn 14336 by default) on every rank of a
+    torchrun launch: token rows sharded, weights replicated, no collective on the data path (weak
+    scaling). --case shard_mlp (dense weights) / shard_mlp_sparse (2:4). One JSON line from rank 0 with
+    the aggregate tokens/s (device time, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from forge_b200 import _forge_C as C
+    from forge_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    m, dm, df = args.m or 8192, args.k or 4096, args.n or 14336
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)   # replicated weights: same seed on every rank
+
+    def qweight(rows, cols):
+        w = torch.randn((rows, cols), generator=g, device=dev) * 0.02
+        return C.prepare_weight(w, sparse=(args.case == "shard_mlp_sparse"))
+
+    packs = [qweight(df, dm), qweight(df, dm), qweight(dm, df)]
+    g.manual_seed(2000 + rank)
+    x = torch.randn((m, dm), generator=g, device=dev, dtype=torch.float16)
+    out = torch.empty((m, dm), dtype=torch.float16, device=dev)
+    ws = torch.empty(lib.forge_w8a8_gated_mlp_workspace_bytes(m, dm, df), dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    scales = [p[3].data_ptr() for p in packs]
+    if args.case == "shard_mlp":
+        fn = lambda: lib.forge_w8a8_gated_mlp(x.data_ptr(), packs[0][0].data_ptr(), packs[1][0].data_ptr(),
+                                              packs[2][0].data_ptr(), *scales, 0, 0, 0, out.data_ptr(), m, dm, df,
+                                              ws.data_ptr(), st)
+    else:
+        wm = []
+        for p in packs:
+            wm += [p[1].data_ptr(), p[2].data_ptr()]
+        fn = lambda: lib.forge_sparse_w8a8_gated_mlp(x.data_ptr(), *wm, *scales, 0, 0, 0, out.data_ptr(), m, dm, df,
+                                                     ws.data_ptr(), st)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        assert fn() == 0
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        assert fn() == 0
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    assert lib.forge_b200_device_status(1) == 0
+    if rank == 0:
+        print(json.dumps({"case": args.case, "n_gpus": world, "scaling": "weak",
+                          "shape": {"tokens_per_gpu": m, "d_model": dm, "d_ffn": df}, "ms": ms,
+                          "tokens_per_s": world * m / (ms * 1e-3),
+                          "dense_equiv_tops": world * 3 * 2.0 * m * dm * df / (ms * 1e-3) / 1e12,
+                          "includes": "quantize -> gate/up GEMM + SiLU gate -> re-quantize -> down GEMM + dequant",
+                          "steps": args.steps}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -582,7 +657,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="headline",
                     help="headline (the contract line) or one kernel: dense, dense_s32, sparse, sparse_s32, "
-                         "quantize, dequant, prune, pack, conv, conv_transpose, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn)")
+                         "quantize, dequant, prune, pack, conv, conv_transpose, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn); "
+                         "under torchrun: shard_rows, shard_cols, shard_mlp, shard_mlp_sparse")
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -606,6 +682,11 @@ def main():
     args = ap.parse_args()
     if args.case in ("shard_rows", "shard_cols"):
         run_sharded_case(args)
+        return
+    if args.case in ("shard_mlp", "shard_mlp_sparse"):
+        if args.steps == 1000:
+            args.steps = 50
+        run_sharded_mlp(args)
         return
     if args.case != "headline":
         run_case(args)
