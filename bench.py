@@ -125,7 +125,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(timed), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-        "config": {"workload": "int8_gemm_dequant M=N=K=8192 (host reference loop on a row sample)",
+        "config": {"workload": "int8_gemm_dequant M=N=K=8192 per GPU (headline shape of the metric)",
+                   "operands": "int8 uniform [-127,127], seeded; fp32 token scales, fp16 channel scales + bias",
                    "sample": sample},
         "cpu_baseline": {"value": tops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
