@@ -115,7 +115,8 @@ def run_reference(args):
     # size the per-step row sample so that warmup + steps take about a minute of host time
     probe, _ = _cpu_baseline(8, 2)
     rows_per_s = 8 / min(probe)
-    rows = int(max(1, min(CPU_SAMPLE_ROWS, rows_per_s * 60.0 / (args.warmup + args.steps))))
+    budget_s = float(os.environ.get("FORGE_B200_REFERENCE_SECONDS", "60"))   # host time for warmup + steps
+    rows = int(max(1, min(CPU_SAMPLE_ROWS, rows_per_s * budget_s / (args.warmup + args.steps))))
     times, cores = _cpu_baseline(rows, args.warmup + args.steps)
     timed = times[args.warmup:]
     total = sum(timed)
