@@ -119,3 +119,66 @@ def test_quantize_converts_a_model(sparse):
     assert y.shape == ref.shape and torch.isfinite(y).all()
     if not sparse:
         assert (y - ref).abs().max() < 0.1 * ref.abs().max() + 0.05
+
+
+def _make_pair():
+    torch.manual_seed(3)
+    w = torch.randn(256, 512)
+    dense = QuantizedLinear(512, 256).to(DEV)
+    dense.quantize_weight(w)
+    sparse = SparseLinear(512, 256).to(DEV)
+    sparse.from_dense_weight(w)
+    dense.bias.data.normal_(0, 0.01)
+    sparse.bias.data.copy_(dense.bias.data)
+    return dense, sparse
+
+
+def test_modules_capture_into_a_cuda_graph():
+    """After one warm-up call (scratch allocated, kernels configured) the forward of both modules is a
+    fixed sequence of launches on the current stream: it captures into a CUDA graph and the replay on
+    new input values gives the eager result."""
+    dense, sparse = _make_pair()
+    for mod in (dense, sparse):
+        mod.eval()
+        x = torch.randn(48, 512, device=DEV, dtype=torch.float16)
+        with torch.no_grad():
+            mod(x)                                   # warm-up
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    y = mod(x)
+            torch.cuda.current_stream().wait_stream(side)
+            x.copy_(torch.randn(48, 512, device=DEV, dtype=torch.float16) * 3)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y, mod(x))
+    assert C.device_status() == 0
+
+
+def test_modules_accept_non_contiguous_and_wider_dtypes():
+    dense, sparse = _make_pair()
+    big = torch.randn(40, 1024, device=DEV, dtype=torch.float16)
+    strided = big[:, ::2]                            # every other column: row stride 1024, element stride 2
+    transposed = torch.randn(512, 40, device=DEV, dtype=torch.float16).t()
+    with torch.no_grad():
+        for mod in (dense, sparse):
+            assert torch.equal(mod(strided), mod(strided.contiguous()))
+            assert torch.equal(mod(transposed), mod(transposed.contiguous()))
+            x32 = torch.randn(8, 512, device=DEV)    # fp32 input is converted to fp16 first
+            assert torch.equal(mod(x32), mod(x32.half()))
+
+
+def test_scratch_buffers_follow_the_batch_size():
+    dense, sparse = _make_pair()
+    with torch.no_grad():
+        for mod in (dense, sparse):
+            outs = {}
+            for m in (4, 64, 16, 200, 4):            # grows, shrinks, grows past the first allocation
+                x = torch.randn(m, 512, device=DEV, dtype=torch.float16)
+                outs[m] = (x, mod(x).clone())
+            fresh_dense, fresh_sparse = _make_pair()
+            fresh = fresh_dense if isinstance(mod, QuantizedLinear) else fresh_sparse
+            for m, (x, y) in outs.items():
+                assert torch.equal(fresh(x), y)
