@@ -44,6 +44,37 @@ def test_prune_compress_pack_exact(N, K):
         assert torch.equal(comp, comp_r) and torch.equal(raw, raw_r) and torch.equal(packed, packed_r)
 
 
+def test_prune_every_order_and_tie_pattern():
+    """Every group of four over an alphabet of 21 byte values (0, +-1, +-2, +-3, +-63, +-64, +-126, +-127,
+    -128 and a few in between: all magnitude orders, every tie shape, both signs, the -128 whose
+    magnitude does not fit a signed byte): 194481 groups, vector and scalar kernels, against the
+    oracle and the reference kernel."""
+    vals = np.array([0, 1, -1, 2, -2, 3, -3, 63, -63, 64, -64, 100, -100, 126, -126, 127, -127, -128, 5, -5, 90], np.int8)
+    grid = np.stack(np.meshgrid(vals, vals, vals, vals, indexing="ij"), axis=-1).reshape(-1, 4)
+    n_groups = grid.shape[0]
+    pad = (-n_groups) % 8
+    grid = np.concatenate([grid, np.zeros((pad, 4), np.int8)])
+    for K in (32, 36):                                   # 36: rows that are not a multiple of 16 bytes
+        rows = (grid.size // K)
+        w = torch.from_numpy(grid.reshape(-1)[:rows * K].reshape(rows, K).copy())
+        comp, raw, _ = _prune_pack(w.to(DEV))
+        comp_cpu, raw_cpu = O.prune_compress_24(w.numpy())
+        assert np.array_equal(comp.cpu().numpy(), comp_cpu)
+        assert np.array_equal(raw.cpu().numpy(), raw_cpu)
+        if O.ref_available() and K % 32 == 0:
+            comp_r, raw_r, _ = O.ref_prune_pack(w.to(DEV))
+            assert torch.equal(comp, comp_r) and torch.equal(raw, raw_r)
+    # the scalar kernel (misaligned compressed output)
+    w = torch.from_numpy(grid.reshape(-1, 32).copy())
+    N, K = w.shape
+    buf = torch.zeros(N * K // 2 + 1, dtype=torch.int8, device=DEV)
+    comp = buf[1:].view(N, K // 2)
+    raw = torch.zeros(N * K // 4, dtype=torch.uint8, device=DEV)
+    C.prune_compress_24(w.to(DEV), comp, raw, N, K)
+    comp_cpu, raw_cpu = O.prune_compress_24(w.numpy())
+    assert np.array_equal(comp.cpu().numpy(), comp_cpu) and np.array_equal(raw.cpu().numpy(), raw_cpu)
+
+
 def test_round_trip_decompress():
     N, K = 64, 256
     g = torch.Generator().manual_seed(5)
