@@ -51,11 +51,56 @@ def scales(M, N, seed):
     return a, w, b
 
 
+def cpu_baselines():
+    """The CPU oracle (OpenMP C restatement of the reference's host loops) on this machine's cores, best of
+    five: the 1024^3 INT32 GEMM in full, per-token quantize and dequant + bias of a 4096 x 4096 activation in
+    full, and a 64-row slice of the 8192^3 GEMM with its linear extrapolation. A reported baseline, not a target."""
+    import time
+
+    import numpy as np
+    rng = np.random.default_rng(1234)
+    threads = ol.oracle().oracle_num_threads()
+    out = [f"| CPU oracle case ({threads} host threads) | best of 5 | rate |", "|---|---|---|"]
+
+    def best(fn):
+        ts = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return min(ts)
+
+    A = rng.integers(-127, 128, (1024, 1024), dtype=np.int8)
+    B = rng.integers(-127, 128, (1024, 1024), dtype=np.int8)
+    t = best(lambda: ol.gemm_s32(A, B))
+    out.append(f"| INT32 GEMM 1024^3 (full) | {t * 1e3:.2f} ms | {2 * 1024 ** 3 / t / 1e12:.4f} TOP/s |")
+    x = rng.standard_normal((4096, 4096)).astype(np.float16)
+    t = best(lambda: ol.quantize(x))
+    out.append(f"| quantize 4096 x 4096 (full) | {t * 1e3:.2f} ms | {(3 * 4096 * 4096 + 4 * 4096) / t / 1e9:.2f} GB/s |")
+    acc = rng.integers(-(1 << 20), 1 << 20, (4096, 4096), dtype=np.int32)
+    a_s = rng.random(4096, dtype=np.float32)
+    w_s = rng.random(4096, dtype=np.float32).astype(np.float16)
+    b = rng.random(4096, dtype=np.float32).astype(np.float16)
+    t = best(lambda: ol.dequantize_bias(acc, a_s, w_s, b))
+    out.append(f"| dequant + bias 4096 x 4096 (full) | {t * 1e3:.2f} ms | {6 * 4096 * 4096 / t / 1e9:.2f} GB/s |")
+    A = rng.integers(-127, 128, (64, 8192), dtype=np.int8)
+    B = rng.integers(-127, 128, (8192, 8192), dtype=np.int8)
+    t = best(lambda: ol.gemm_s32(A, B))
+    out.append(f"| INT32 GEMM 8192^3, 64-row slice | {t * 1e3:.1f} ms | {2 * 64 * 8192 ** 2 / t / 1e12:.4f} TOP/s "
+               f"(whole GEMM extrapolated linearly: {t * 128:.1f} s) |")
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--cpu", type=int, default=1, help="also time the CPU oracle on this host (reported baseline)")
+    ap.add_argument("--only-cpu", type=int, default=0, help="print the CPU oracle timings and stop")
     args = ap.parse_args()
+    if args.only_cpu:
+        print("\n".join(cpu_baselines()))
+        return
     if not ol.ref_available():
         raise SystemExit("oracle/_ref/libforge_ref.so is not built")
     torch.cuda.set_device(0)
@@ -171,6 +216,13 @@ def main():
         report("int8_conv_transpose2d_k2s2", f"N={N} C_in={Ci} {H}x{W} C_out={Co}", "GB/s (input + output bytes)",
                (2.0 * x.numel() + 2.0 * o_new.numel() + wt.numel()) / 1e6, t_ref, t_new, torch.equal(o_ref, o_new))
         del x, o_ref, o_new, ws
+
+    if args.cpu:
+        cpu_rows = cpu_baselines()
+        print("\n".join(cpu_rows))
+        if args.out:
+            with open(args.out + ".cpu.md", "w") as f:
+                f.write("\n".join(cpu_rows) + "\n")
 
     lines = ["| entry point | shape | reference kernel on B200 | this library | unit | speed-up | bit-identical |",
              "|---|---|---|---|---|---|---|"]
