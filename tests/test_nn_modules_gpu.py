@@ -182,3 +182,27 @@ def test_scratch_buffers_follow_the_batch_size():
             fresh = fresh_dense if isinstance(mod, QuantizedLinear) else fresh_sparse
             for m, (x, y) in outs.items():
                 assert torch.equal(fresh(x), y)
+
+
+def test_static_scheme_calibration_and_qat_flow_on_the_gpu():
+    """quantize(model, data, scheme="static_int8") runs the calibration batches through the converted
+    model (the reference's call shape), and prepare_qat -> enable_qat -> finalize_qat ends in layers
+    whose output equals a direct conversion of the same float weights."""
+    from forge_b200 import quant as Q
+    torch.manual_seed(4)
+    model = TinyMLP().to(DEV).half()
+    data = [torch.randn(8, 256, device=DEV, dtype=torch.float16) for _ in range(3)]
+    q_static = Q.quantize(model, data, 2, "static_int8", verbose=False)
+    q_dyn = Q.quantize(model, verbose=False)
+    x = torch.randn(16, 256, device=DEV, dtype=torch.float16)
+    with torch.no_grad():
+        assert torch.equal(q_static(x), q_dyn(x))
+    qat = Q.prepare_qat(model.float())
+    Q.enable_calibration(qat)
+    with torch.no_grad():
+        qat(x.float())
+    Q.enable_qat(qat)
+    qat(x.float()).sum().backward()
+    final = Q.finalize_qat(qat, verbose=False)
+    with torch.no_grad():
+        assert torch.equal(final(x), q_dyn(x))
