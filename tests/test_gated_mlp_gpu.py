@@ -9,7 +9,6 @@ evaluates SiLU in fp32 with approximate exp/divide, so h is required to be withi
 that; everything downstream of the GPU's own h (re-quantize, down GEMM, dequant) is required to be
 bit-exact, and the sparse kernels must agree bit for bit with the dense kernel run on the
 zero-filled pruned weights."""
-import ctypes
 
 import numpy as np
 import pytest
