@@ -93,6 +93,8 @@ def _cpu_baseline(rows, reps):
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as O
+    # all the cores this process may run on, whatever OMP_NUM_THREADS a launcher exported
+    O.oracle().oracle_set_num_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(1234)
     A = rng.integers(-127, 128, (rows, K), dtype=np.int8)
     B = rng.integers(-127, 128, (N, K), dtype=np.int8)

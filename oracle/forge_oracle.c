@@ -346,6 +346,16 @@ void oracle_conv_transpose_k2s2_scatter(const uint16_t* gemm_out, const uint16_t
                 }
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1 for every rank; a baseline that is meant to use
+ * the host's cores sets the count explicitly. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -43,6 +43,7 @@ def oracle():
         lib.oracle_int8_conv2d.argtypes = [_vp] * 5 + [_i] * 13
         lib.oracle_conv_transpose_k2s2_scatter.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i]
         lib.oracle_num_threads.restype = _i
+        lib.oracle_set_num_threads.argtypes = [_i]
         _oracle = lib
     return _oracle
 

@@ -9,7 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_reference_arm_prints_one_contract_line():
-    env = dict(os.environ, FORGE_B200_REFERENCE_SECONDS="3")
+    env = dict(os.environ, FORGE_B200_REFERENCE_SECONDS="3", OMP_NUM_THREADS="1")   # as torchrun exports it
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "3",
                         "--warmup", "3"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
     assert r.returncode == 0, r.stderr
@@ -19,7 +19,8 @@ def test_reference_arm_prints_one_contract_line():
     assert d["impl"] == "reference" and d["unit"] == "TOPS" and d["higher_is_better"] is True
     assert d["metric"] == "int8_gemm_dequant_tops_m8192_n8192_k8192"
     assert d["steps"] == 3 and d["warmup"] == 3 and d["n_gpus"] == 1 and d["value"] > 0
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["sample"]
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))    # not the launcher's single thread
     assert d["e2e"] == {"value": d["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["gpu_launches"] == 0 and "workload" in d["config"]
 
