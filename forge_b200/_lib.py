@@ -45,12 +45,20 @@ SIGNATURES = {
     "forge_int8_conv2d_forward": [_vp] * 5 + [_i] * 13 + [_vp, _vp],
     "forge_int8_conv_transpose2d_k2s2_workspace_size": [_i] * 4,
     "forge_int8_conv_transpose2d_k2s2_forward": [_vp] * 5 + [_i] * 5 + [_vp, _vp],
-    "forge_b200_set_dense_tile": [_i],
-    "forge_b200_set_sparse_tile": [_i],
     "forge_b200_device_status": [_i],
+    "forge_b200_device_status_raw": [_i],
     "forge_b200_status_string": [_i],
 }
-_VOID_RETURN = {"forge_b200_set_dense_tile", "forge_b200_set_sparse_tile"}
+# exported test / tuning hooks that are not part of the public header (csrc/tuning.h)
+INTERNAL_SIGNATURES = {
+    "forge_b200_set_dense_tile": [_i],
+    "forge_b200_set_sparse_tile": [_i],
+    "forge_b200_set_tuning": [_i, _i],
+    "forge_b200_get_tuning": [_i],
+    "forge_b200_selftest_wait_timeout": [ctypes.c_uint, _vp],
+    "forge_b200_read_probe": [_vp, _i],
+}
+_VOID_RETURN = {"forge_b200_set_dense_tile", "forge_b200_set_sparse_tile", "forge_b200_set_tuning"}
 
 _lib = None
 
@@ -69,7 +77,7 @@ def load():
             f"{LIB_PATH} not found: build it with `python -m forge_b200.build` (needs nvcc). "
             "forge_b200 has no CPU or PyTorch fallback.")
     lib = ctypes.CDLL(LIB_PATH)
-    for name, argtypes in SIGNATURES.items():
+    for name, argtypes in list(SIGNATURES.items()) + list(INTERNAL_SIGNATURES.items()):
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         if name in _VOID_RETURN:

@@ -12,8 +12,8 @@ using namespace fb200;
 
 namespace {
 
-int g_force_dense_bn = 0;
-int g_force_sparse_bt = 0;
+inline int force_dense_bn() { return tuning_knob(kKnobDenseTile); }
+inline int force_sparse_bt() { return tuning_knob(kKnobSparseTile); }
 
 inline cudaStream_t S(forge_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 inline const __half* H(const void* p) { return static_cast<const __half*>(p); }
@@ -21,14 +21,20 @@ inline __half* H(void* p) { return static_cast<__half*>(p); }
 
 // Tile id of the reference API -> tile knob of the tcgen05 kernels: the reference's 256-row
 // weight tile is the CTA-pair kernel (256 weight rows x 224 tokens per pair, knob 1000 + 224);
-// its 128-row tiles are the single-CTA kernel with 128 / 64 tokens.
-inline int tile_to_bt(int tile) {
+// its 128-row tiles are the single-CTA kernel with 128 tokens, or 64 (32 when M <= 32) tokens.
+inline int tile_to_bt(int tile, int M) {
     switch (tile) {
     case FORGE_SPARSE_TILE_256x128: return 1224;
     case FORGE_SPARSE_TILE_128x128: return 128;
-    case FORGE_SPARSE_TILE_128x64: return 64;
+    case FORGE_SPARSE_TILE_128x64: return M <= 32 ? 32 : 64;
     default: return 0;
     }
+}
+
+inline int choice_to_tile(const SparseChoice& c) {
+    if (c.kind == 2) return FORGE_SPARSE_TILE_256x128;
+    if (c.kind == 1 && c.bt == 128) return FORGE_SPARSE_TILE_128x128;
+    return FORGE_SPARSE_TILE_128x64;
 }
 
 // fp32 workspace + bias -> fp16, the contract of the reference's splitk_reduce_kernel
@@ -58,7 +64,7 @@ int forge_fused_dequantize_bias(const int32_t* input, const float* act_scale, co
 
 int forge_int8_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
                             const void* bias, void* output, int M, int K, int N, forge_stream_t stream) {
-    return dense_gemm_dequant(A, B, act_scale, H(w_scale), H(bias), H(output), M, K, N, S(stream), g_force_dense_bn);
+    return dense_gemm_dequant(A, B, act_scale, H(w_scale), H(bias), H(output), M, K, N, S(stream), force_dense_bn());
 }
 
 int forge_int8_gemm(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale, const void* bias,
@@ -77,7 +83,7 @@ int forge_int8_linear(const void* x, const int8_t* w_int8, const void* w_scale, 
     const int r = quantize_activation(H(x), scratch_a_int8, scratch_a_scale, M, K, S(stream));
     if (r != kOk) return r;
     return dense_gemm_dequant(scratch_a_int8, w_int8, scratch_a_scale, H(w_scale), H(bias), H(output), M, K, N,
-                              S(stream), g_force_dense_bn);
+                              S(stream), force_dense_bn());
 }
 
 int forge_int8_dp4a_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
@@ -97,26 +103,19 @@ int forge_has_wmma_int8(int device) { return forge_get_compute_capability(device
 
 int forge_int8_gemm_s32(const int8_t* A, const int8_t* B, int32_t* output, int M, int K, int N,
                         forge_stream_t stream) {
-    return dense_gemm_s32(A, B, output, M, K, N, S(stream), g_force_dense_bn);
+    return dense_gemm_s32(A, B, output, M, K, N, S(stream), force_dense_bn());
 }
 
 int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_workspace, int tile, int* out_tile,
                                 int* out_split_k) {
-    (void)K;
-    if (tile >= FORGE_SPARSE_NUM_TILES) tile = FORGE_SPARSE_TILE_AUTO;
-    int t = tile;
-    if (t < 0) {
-        // automatic: the CTA-pair kernel for large problems, else 128-token tiles once they give
-        // every SM work, else 64-token tiles (mirrors sparse_dispatch in gemm_sparse.cu)
-        const long long w_blocks = (N_out + 127) / 128;
-        if (M >= 1024 && N_out >= 512) t = FORGE_SPARSE_TILE_256x128;
-        else t = (M > 64 && w_blocks * ((M + 127) / 128) >= sm_count()) ? FORGE_SPARSE_TILE_128x128
-                                                                         : FORGE_SPARSE_TILE_128x64;
-    }
     // The K loop is never split: the exact s32 accumulation in TMEM covers the whole K range.
     (void)split_k;
     (void)have_workspace;
-    if (out_tile) *out_tile = t;
+    if (tile >= FORGE_SPARSE_NUM_TILES) tile = FORGE_SPARSE_TILE_AUTO;   // reference: int8_sparse.cu:895
+    int bt = force_sparse_bt();
+    if (bt == 0 && tile >= 0) bt = tile_to_bt(tile, M);
+    const SparseChoice c = sparse_choose(M, K, N_out, K % 128 == 0, bt, true);
+    if (out_tile) *out_tile = choice_to_tile(c);
     if (out_split_k) *out_split_k = 1;
     return kOk;
 }
@@ -126,8 +125,8 @@ int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uin
                            int N_out, float* splitk_workspace, int split_k, forge_stream_t stream, int tile) {
     (void)splitk_workspace;
     (void)split_k;
-    int bt = g_force_sparse_bt;
-    if (bt == 0 && tile >= 0 && tile < FORGE_SPARSE_NUM_TILES) bt = tile_to_bt(tile);
+    int bt = force_sparse_bt();
+    if (bt == 0 && tile >= 0 && tile < FORGE_SPARSE_NUM_TILES) bt = tile_to_bt(tile, M);
     return sparse_gemm_dequant(W_comp, x_int8, w_meta, act_scale, H(w_scale), H(bias), H(output), M, K, N_out,
                                S(stream), bt);
 }
@@ -176,7 +175,7 @@ int forge_splitk_reduce(const float* workspace, const void* bias, void* output, 
 
 int forge_sparse_int8_gemm_s32(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta, int32_t* output,
                                int M, int K, int N_out, forge_stream_t stream) {
-    return sparse_gemm_s32(W_comp, x_int8, w_meta, output, M, K, N_out, S(stream), g_force_sparse_bt);
+    return sparse_gemm_s32(W_comp, x_int8, w_meta, output, M, K, N_out, S(stream), force_sparse_bt());
 }
 
 int forge_sparse_int8_gemm_multi(const int8_t* W_comp, const int8_t* x_int8, const uint32_t* w_meta,
@@ -198,7 +197,7 @@ int forge_sparse_int8_gated_gemm(const int8_t* Wg_comp, const uint32_t* wg_meta,
                                  const void* wg_scale, const void* wu_scale, const void* bg, const void* bu,
                                  void* h_out, int M, int K, int N_out, forge_stream_t stream) {
     return sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, x_int8, act_scale, H(wg_scale), H(wu_scale), H(bg),
-                             H(bu), H(h_out), M, K, N_out, S(stream), g_force_sparse_bt);
+                             H(bu), H(h_out), M, K, N_out, S(stream), force_sparse_bt());
 }
 
 namespace {
@@ -253,7 +252,7 @@ int forge_w8a8_gated_mlp(const void* x, const int8_t* Wg, const int8_t* Wu, cons
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;
     return dense_gemm_dequant(w.hq, Wd, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
-                              g_force_dense_bn);
+                              force_dense_bn());
 }
 
 int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint32_t* wg_meta, const int8_t* Wu_comp,
@@ -267,12 +266,12 @@ int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint
     int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
     if (r != kOk) return r;
     r = sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, w.xq, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h,
-                          M, d_model, d_ffn, S(stream), g_force_sparse_bt);
+                          M, d_model, d_ffn, S(stream), force_sparse_bt());
     if (r != kOk) return r;
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;
     return sparse_gemm_dequant(Wd_comp, w.hq, wd_meta, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
-                               g_force_sparse_bt);
+                               force_sparse_bt());
 }
 
 int forge_prune_compress_24(const int8_t* weight, int8_t* compressed, uint8_t* metadata_raw, int N, int K,
@@ -317,11 +316,6 @@ int forge_int8_conv_transpose2d_k2s2_forward(const void* input, const int8_t* we
                                               static_cast<__half*>(output), N, C_in, H, W, C_out,
                                               S(stream));
 }
-
-void forge_b200_set_dense_tile(int bn) { g_force_dense_bn = bn; }
-void forge_b200_set_sparse_tile(int bt) { g_force_sparse_bt = bt; }
-
-int forge_b200_device_status(int reset) { return read_device_status(reset); }
 
 const char* forge_b200_status_string(int status) {
     switch (status) {

@@ -26,4 +26,15 @@ int* status_word();
 // Reads the status word back (synchronising copy); clears it when reset != 0. -1 on failure.
 int read_device_status(int reset);
 
+// Process-wide integer knobs (tuning.h); 0 = default behaviour.
+enum TuningKnob : int {
+    kKnobDenseTile = 0,        // pinned dense tile width
+    kKnobSparseTile = 1,       // pinned sparse token-tile width
+    kKnobMaxPairs = 2,         // CTA-pair kernels: launch at most this many pairs
+    kKnobPairFlags = 3,        // CTA-pair kernels, measurement only: bit 0 = operands stay resident after the
+                               // first ring fill (wrong results; tensor-core side alone), bit 1 = one commit
+                               // per CTA to free a stage, bit 2 = sparse MMA thread records its wait clocks
+};
+int tuning_knob(int key);
+
 }  // namespace fb200

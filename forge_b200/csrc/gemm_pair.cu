@@ -9,12 +9,20 @@
 // bytes a CTA has to pull from L2, which is what limits the single-CTA kernels.
 //
 // Barrier protocol (per pipeline stage s; "leader" = cluster rank 0):
-//   full[s]   lives in the leader. The leader's producer arms it with the byte count of both
-//             CTAs' loads; every TMA load of either CTA reports its bytes to it.
-//   empty[s]  one per CTA. The leader's MMA thread commits to both after the MMAs that read
-//             stage s, each CTA's producer waits on its own.
+//   full[s]   lives in the leader. The leader's first producer arms it with the byte count of both
+//             CTAs' operand loads; every operand TMA load of either CTA reports its bytes to it.
+//   empty[s]  one per CTA. After the MMAs that read stage s the leader's MMA thread issues ONE
+//             tcgen05.commit whose arrival is delivered to the barrier at the same shared-memory
+//             offset in both CTAs; each CTA's producers wait on their own. (Two commits, one per
+//             CTA, cost the sparse MMA stream about 70 clocks each - measured.)
 //   tmem_full[b]  one per CTA, committed by the leader after a tile's last MMA.
-//   tmem_empty[b] lives in the leader; the 4 + 4 epilogue warps of both CTAs arrive on it.
+//   tmem_empty[b] lives in the leader; the epilogue warps of both CTAs arrive on it.
+//   sparse kernel only:
+//   meta_full[s]  lives in the leader; armed with the bytes of both CTAs' metadata slabs, which
+//                 report to it instead of full[s].
+//   meta_ready[s] lives in the leader; committed by the metadata-copy thread (below) once the
+//                 slab is in tensor memory AND full[s] has completed - the only barrier the MMA
+//                 thread waits on per stage.
 // Every wait is bounded; a wait that runs out sets the CTA's abort flag and the device status
 // word, and all roles fall through to the common teardown (cluster barrier, TMEM free).
 #include "common.cuh"
@@ -29,13 +37,14 @@ using namespace ptx;
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;   // TMA warp, MMA warp, 4 epilogue warps, second TMA warp
 constexpr int kEpiWarps = 4;
 constexpr int kEpiThreads = 128;
 // sparse kernel: epilogue warps per CTA - two per TMEM lane quarter, four for the gated epilogue
 // (measured: the heavier SiLU epilogue gains from 16 warps, the plain one loses a little)
 __host__ __device__ constexpr int sp_epi_warps(int epi) { return epi == 2 ? 16 : 8; }
-__host__ __device__ constexpr int sp_threads(int epi) { return 64 + 32 * sp_epi_warps(epi); }
+// TMA warp, MMA warp, the epilogue warps, second TMA warp
+__host__ __device__ constexpr int sp_threads(int epi) { return 128 + 32 * sp_epi_warps(epi); }
 constexpr int kSpEpiWarpsMax = 16;
 // weight-row blocks per raster band of the sparse kernel: the activations are re-read from DRAM
 // once per band, the band's weights stay in L2
@@ -49,6 +58,8 @@ struct PairBars {
     uint64_t* empty;       // [stages]
     uint64_t* tmem_full;   // [2]
     uint64_t* tmem_empty;  // [2], used in the leader
+    uint64_t* meta_full;   // [stages], used in the leader (sparse kernel)
+    uint64_t* meta_ready;  // [stages], used in the leader (sparse kernel)
     uint32_t* tmem_slot;
     volatile int* abort_flag;
 };
@@ -60,7 +71,9 @@ __device__ __forceinline__ PairBars carve_bars(uint8_t* p, int stages) {
     b.empty = q + stages;
     b.tmem_full = q + 2 * stages;
     b.tmem_empty = b.tmem_full + 2;
-    b.tmem_slot = reinterpret_cast<uint32_t*>(b.tmem_empty + 2);
+    b.meta_full = b.tmem_empty + 2;
+    b.meta_ready = b.meta_full + stages;
+    b.tmem_slot = reinterpret_cast<uint32_t*>(b.meta_ready + stages);
     b.abort_flag = reinterpret_cast<volatile int*>(b.tmem_slot + 1);
     return b;
 }
@@ -69,6 +82,8 @@ __device__ __forceinline__ void init_bars(const PairBars& b, int stages, int epi
     for (int s = 0; s < stages; s++) {
         mbar_init(&b.full[s], 1);
         mbar_init(&b.empty[s], 1);
+        mbar_init(&b.meta_full[s], 1);
+        mbar_init(&b.meta_ready[s], 1);
     }
     for (int i = 0; i < 2; i++) {
         mbar_init(&b.tmem_full[i], 1);
@@ -77,6 +92,17 @@ __device__ __forceinline__ void init_bars(const PairBars& b, int stages, int epi
     *b.abort_flag = 0;
     fence_mbar_init();
 }
+
+// Launch flags (measurement only; 0 in normal operation).
+constexpr int kFlagResident = 1;    // stop loading after the first ring fill: the MMAs re-read resident stages
+                                    // (wrong results; the time of the tensor-core side alone)
+constexpr int kFlagTwoCommits = 2;  // free a stage with one tcgen05.commit per CTA instead of one commit
+                                    // delivered to both CTAs' barriers
+constexpr int kFlagProbe = 4;       // sparse: pair 0's MMA thread records where its clocks go (g_pair_probe)
+
+// kFlagProbe: [0] total clocks of the MMA thread's loop, [1] waiting for operands, [2] waiting for a
+// drained accumulator, [3] stages, [4] tiles
+__device__ unsigned long long g_pair_probe[8];
 
 struct TileCoord {
     int a_blk, b_blk;   // block index along the M-side operand / the N-side operand
@@ -119,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ act_scale,
                   const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
-                  int* __restrict__ status) {
+                  int* __restrict__ status, int flags) {
     using Cfg = DensePairCfg;
     constexpr int BN = 256;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -161,15 +187,19 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *bars.tmem_slot;
 
-    if (warp_id == 0) {
-        // ------------------------------------------------------------------ TMA producer (both CTAs)
+    // Two TMA producers per CTA: warp 0 loads the A slab and arms the stage's barrier with the byte
+    // count of the whole stage (both CTAs), the last warp loads the B slab.
+    const bool second = (warp_id == kThreads / 32 - 1);
+    if (warp_id == 0 || second) {
+        // ------------------------------------------------------------------ TMA producers (both CTAs)
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            int it = 0;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const TileCoord tc = tile_coord(t, m_blocks, n_blocks, kDenseBand);
-                for (int kb = 0; kb < num_kb; kb++) {
+                for (int kb = 0; kb < num_kb; kb++, it++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
                         atomicExch(status, 301);
                         ok = false;
@@ -177,10 +207,15 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                     uint8_t* sa = smem_ab + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
                     const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
-                    tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
-                    tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
+                    if ((flags & kFlagResident) != 0 && it >= Cfg::kStages) {
+                        if (leader && !second) mbar_arrive(&bars.full[stage]);
+                    } else if (!second) {
+                        if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
+                        tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
+                    } else {
+                        tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
+                    }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -220,8 +255,12 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int k = 0; k < 4; k++)
                         umma_i8_pair(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     const uint32_t e = smem_u32(&bars.empty[stage]);
-                    tc_commit_pair(mapa_shared(e, 0));
-                    tc_commit_pair(mapa_shared(e, 1));
+                    if ((flags & kFlagTwoCommits) == 0) {
+                        tc_commit_pair_mask(e, 3);
+                    } else {
+                        tc_commit_pair(mapa_shared(e, 0));
+                        tc_commit_pair(mapa_shared(e, 1));
+                    }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -378,7 +417,8 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
-                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
+                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status,
+                   int flags) {
     // EPI 2 (gated): each CTA's 128-row weight tile is 64 gate rows followed by the 64 up rows of the
     // same output columns, so a pair produces 128 output columns per tile.
     using Cfg = SparsePairCfg<BT, EPI>;
@@ -425,17 +465,23 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t tmem_base = *bars.tmem_slot;
     const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
 
-    if (warp_id == 0) {
-        // ------------------------------------------------------------------ TMA producer (both CTAs)
+    // Two TMA producers per CTA: warp 0 loads the weight slab and its metadata and arms the stage's
+    // barriers with the byte counts of both CTAs; the second-to-last warp loads the two activation
+    // atoms.
+    const bool second = (warp_id == sp_threads(EPI) / 32 - 2);
+    const bool copy_warp = (warp_id == sp_threads(EPI) / 32 - 1);
+    if (warp_id == 0 || second) {
+        // ------------------------------------------------------------------ TMA producers (both CTAs)
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            int it = 0;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
                 const int w_row = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W;
                 const int t_row = tc.b_blk * BT + (int)rank * HT;
-                for (int kb = 0; kb < num_kb; kb++) {
+                for (int kb = 0; kb < num_kb; kb++, it++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
                         atomicExch(status, 401);
                         ok = false;
@@ -444,22 +490,34 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
                     uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
-                    if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
                     const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
-                    if (EPI == 2) {
-                        tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
-                        tma_load_2d_pair(sa + Cfg::kABytes / 2, &tm_w2, full_leader, kb * 128, w_row);
+                    const uint32_t meta_leader = mapa_shared(smem_u32(&bars.meta_full[stage]), 0);
+                    if ((flags & kFlagResident) != 0 && it >= Cfg::kStages) {
+                        if (leader && !second) {
+                            mbar_arrive(&bars.meta_full[stage]);
+                            mbar_arrive(&bars.full[stage]);
+                        }
+                    } else if (!second) {
+                        if (leader) {
+                            mbar_expect_tx(&bars.meta_full[stage], 2 * Cfg::kMetaBytes);
+                            mbar_expect_tx(&bars.full[stage], 2 * (Cfg::kStageBytes - Cfg::kMetaBytes));
+                        }
+                        if (EPI == 2) {
 #pragma unroll
-                        for (int c = 0; c < 2; c++) {
-                            tma_load_3d_pair(sm + c * 2048, &tm_meta, full_leader, 0, w_row, kb * 2 + c);
-                            tma_load_3d_pair(sm + c * 2048 + 1024, &tm_meta2, full_leader, 0, w_row, kb * 2 + c);
+                            for (int c = 0; c < 2; c++) {
+                                tma_load_3d_pair(sm + c * 2048, &tm_meta, meta_leader, 0, w_row, kb * 2 + c);
+                                tma_load_3d_pair(sm + c * 2048 + 1024, &tm_meta2, meta_leader, 0, w_row, kb * 2 + c);
+                            }
+                            tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
+                            tma_load_2d_pair(sa + Cfg::kABytes / 2, &tm_w2, full_leader, kb * 128, w_row);
+                        } else {
+                            tma_load_3d_pair(sm, &tm_meta, meta_leader, 0, w_row, kb * 2);
+                            tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
                         }
                     } else {
-                        tma_load_2d_pair(sa, &tm_w, full_leader, kb * 128, w_row);
-                        tma_load_3d_pair(sm, &tm_meta, full_leader, 0, w_row, kb * 2);
+                        tma_load_2d_pair(sb, &tm_x, full_leader, kb * 256, t_row);
+                        tma_load_2d_pair(sb + Cfg::kBAtomBytes, &tm_x, full_leader, kb * 256 + 128, t_row);
                     }
-                    tma_load_2d_pair(sb, &tm_x, full_leader, kb * 256, t_row);
-                    tma_load_2d_pair(sb + Cfg::kBAtomBytes, &tm_x, full_leader, kb * 256 + 128, t_row);
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -474,30 +532,36 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
+            int it = 0;
             bool ok = true;
+            const bool probe = (flags & kFlagProbe) != 0 && pair_id == 0;
+            long long wait_ops = 0, wait_acc = 0;
+            const long long t_begin = probe ? clock64() : 0;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs, local++) {
                 const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
                 const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                long long w0 = probe ? clock64() : 0;
                 if (!mbar_wait(&bars.tmem_empty[buf], acc_phase ^ 1, bars.abort_flag)) {
                     atomicExch(status, 402);
                     ok = false;
                     break;
                 }
+                if (probe) wait_acc += clock64() - w0;
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + buf * BT;
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&bars.full[stage], phase, bars.abort_flag)) {
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    w0 = probe ? clock64() : 0;
+                    // meta_ready[s]: the stage's metadata is in tensor memory and its operand loads have landed
+                    if (!mbar_wait(&bars.meta_ready[stage], phase, bars.abort_flag)) {
                         atomicExch(status, 403);
                         ok = false;
                         break;
                     }
+                    if (probe) wait_ops += clock64() - w0;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_stage + stage * Cfg::kStageBytes);
                     const uint32_t sb = sa + Cfg::kABytes;
-                    const uint32_t sm = sb + 2 * Cfg::kBAtomBytes;
                     const uint32_t te = tmem_meta + 8 * stage;
-                    tmem_cp_128x128b_pair(te, make_desc_noswizzle(sm, 2048, 128));
-                    tmem_cp_128x128b_pair(te + 4, make_desc_noswizzle(sm + 2048, 2048, 128));
                     const uint64_t desc_a = make_desc_sw128(sa);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -505,8 +569,12 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                         umma_i8_sp_pair(tmem_acc, desc_a + 2 * j, desc_b, te + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
                     const uint32_t e = smem_u32(&bars.empty[stage]);
-                    tc_commit_pair(mapa_shared(e, 0));
-                    tc_commit_pair(mapa_shared(e, 1));
+                    if ((flags & kFlagTwoCommits) == 0) {
+                        tc_commit_pair_mask(e, 3);
+                    } else {
+                        tc_commit_pair(mapa_shared(e, 0));
+                        tc_commit_pair(mapa_shared(e, 1));
+                    }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -516,6 +584,49 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     const uint32_t f = smem_u32(&bars.tmem_full[buf]);
                     tc_commit_pair(mapa_shared(f, 0));
                     tc_commit_pair(mapa_shared(f, 1));
+                }
+            }
+            if (probe) {
+                g_pair_probe[0] = (unsigned long long)(clock64() - t_begin);
+                g_pair_probe[1] = (unsigned long long)wait_ops;
+                g_pair_probe[2] = (unsigned long long)wait_acc;
+                g_pair_probe[3] = (unsigned long long)it;
+                g_pair_probe[4] = (unsigned long long)local;
+            }
+        }
+    } else if (copy_warp) {
+        // ------------------------------------------------------------------ metadata copies (leader only)
+        // A thread of its own moves each stage's metadata slab (both CTAs' 128 rows x 32 bytes) into
+        // tensor memory with one tcgen05.cp as soon as the slab has landed - while the stage's
+        // operand loads are still in flight - and commits to meta_ready[s] after full[s]. Issued from
+        // the MMA thread instead, the copies sit in the MMA stream and cost about a fifth of the
+        // kernel's time (measured at 8192^3).
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&bars.meta_full[stage], phase, bars.abort_flag)) {
+                        atomicExch(status, 405);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sm = smem_u32(smem_stage + stage * Cfg::kStageBytes) + Cfg::kABytes +
+                                        2 * Cfg::kBAtomBytes;
+                    // two 16-byte columns of 128 rows -> 8 TMEM columns
+                    tmem_cp_128x256b_pair(tmem_meta + 8 * stage, make_desc_noswizzle(sm, 2048, 128));
+                    if (!mbar_wait(&bars.full[stage], phase, bars.abort_flag)) {
+                        atomicExch(status, 406);
+                        ok = false;
+                        break;
+                    }
+                    tc_commit_pair(mapa_shared(smem_u32(&bars.meta_ready[stage]), 0));
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
                 }
             }
         }
@@ -700,7 +811,9 @@ int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaSt
         }
     }
     if (max_pairs < 0) return -1;
-    const int pairs = (int)std::min<long long>(tiles, max_pairs);
+    int pairs = (int)std::min<long long>(tiles, max_pairs);
+    const int cap = tuning_knob(kKnobMaxPairs);
+    if (cap > 0 && cap < pairs) pairs = cap;
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
     return e == cudaSuccess ? kOk : kLaunchFailed;
@@ -737,7 +850,7 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
     return launch_pairs(dense_pair_kernel<EPI>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b, tm_c,
-                        act_scale, w_scale, bias, M, N, K, status);
+                        act_scale, w_scale, bias, M, N, K, status, tuning_knob(kKnobPairFlags));
 }
 
 template <int BT, int EPI>
@@ -785,7 +898,7 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     if (multi != nullptr) md = *multi;
     return launch_pairs(sparse_pair_kernel<BT, EPI>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
                         tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
-                        status);
+                        status, tuning_knob(kKnobPairFlags));
 }
 
 template <int EPI>
@@ -801,6 +914,11 @@ int sparse_pair_dispatch(int bt, const int8_t* W_comp, const int8_t* x, const ui
 }
 
 }  // namespace
+
+int read_pair_probe(unsigned long long* out, int n) {
+    if (n > 8) n = 8;
+    return cudaMemcpyFromSymbol(out, g_pair_probe, sizeof(unsigned long long) * n) == cudaSuccess ? kOk : kLaunchFailed;
+}
 
 int dense_pair_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K, int N, cudaStream_t stream) {
     return launch_dense_pair<0>(A, B, nullptr, nullptr, nullptr, out, M, K, N, stream);

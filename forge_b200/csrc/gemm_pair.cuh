@@ -19,6 +19,9 @@ int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int bt);
 
+// Copies the sparse pair kernel's probe counters (pair-kernel flag 32) to `out`.
+int read_pair_probe(unsigned long long* out, int n);
+
 struct OutDst;
 // FP16 result written to every destination in `multi` (see sparse_epilogue.cuh).
 int sparse_pair_dequant_multi(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,

@@ -442,23 +442,34 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
             W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
     }
-    // 1000 + BT: the CTA-pair kernel (256 weight rows x BT tokens per pair of SMs).
-    if (force_bt > 1000) {
+    SparseChoice c = sparse_choose(M, K, N_out, true, force_bt, true);
+    if (c.kind == 2) {
         const int r = (EPI == 0) ? sparse_pair_s32(W_comp, x, w_meta, static_cast<int32_t*>(out), M, K, N_out,
-                                                   stream, force_bt - 1000)
+                                                   stream, c.bt)
                                  : sparse_pair_dequant(W_comp, x, w_meta, act_scale, w_scale, bias,
-                                                       static_cast<__half*>(out), M, K, N_out, stream,
-                                                       force_bt - 1000);
+                                                       static_cast<__half*>(out), M, K, N_out, stream, c.bt);
         if (r >= 0) return r;
+        c = sparse_choose(M, K, N_out, true, force_bt, false);   // no pair of these CTAs fits on this device
     }
-    // Large problems: 256 weight rows x 224 tokens per CTA pair (measured fastest from M = N_out = 8192,
-    // K >= 1024 down to the 11008 x 4096 weight of a Llama MLP).
-    if (force_bt == 0 && M >= 1024 && N_out >= 512) {
-        const int r = (EPI == 0) ? sparse_pair_s32(W_comp, x, w_meta, static_cast<int32_t*>(out), M, K, N_out,
-                                                   stream, 224)
-                                 : sparse_pair_dequant(W_comp, x, w_meta, act_scale, w_scale, bias,
-                                                       static_cast<__half*>(out), M, K, N_out, stream, 224);
-        if (r >= 0) return r;
+    const int bt = c.bt;
+    switch (bt) {
+    case 128: return launch_sparse<128, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    case 64:  return launch_sparse<64, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    default:  return launch_sparse<32, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
+    }
+}
+
+}  // namespace
+
+SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, int force_bt, bool allow_pair) {
+    (void)K;
+    if (!tma_ok) return {0, 0};
+    if (allow_pair) {
+        // 1000 + BT: the CTA-pair kernel (256 weight rows x BT tokens per pair of SMs), pinned.
+        if (force_bt > 1000) return {2, force_bt - 1000};
+        // Large problems: 256 weight rows x 224 tokens per CTA pair (measured fastest from
+        // M = N_out = 8192, K >= 1024 down to the 11008 x 4096 weight of a Llama MLP).
+        if (force_bt == 0 && M >= 1024 && N_out >= 512) return {2, 224};
     }
     int bt = force_bt;
     if (bt != 32 && bt != 64 && bt != 128) {
@@ -468,14 +479,8 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
         else if (M > 32) bt = (M > 64 && w_blocks * ((M + 63) / 64) < sms) ? 64 : (M > 64 ? 128 : 64);
         else bt = 32;
     }
-    switch (bt) {
-    case 128: return launch_sparse<128, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
-    case 64:  return launch_sparse<64, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
-    default:  return launch_sparse<32, EPI>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream);
-    }
+    return {1, bt};
 }
-
-}  // namespace
 
 int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,
                     int N_out, cudaStream_t stream, int force_bt) {

@@ -6,6 +6,17 @@
 
 namespace fb200 {
 
+// Which kernel a 2:4-sparse GEMM call runs: decided in one place for the GEMM's own dispatch and
+// for the public plan query (forge_sparse_int8_gemm_plan).
+struct SparseChoice {
+    int kind;   // 0 = plain-CUDA kernel (shapes TMA cannot describe), 1 = one CTA per tile, 2 = CTA pair
+    int bt;     // tokens per tile (kind 1: 32 / 64 / 128; kind 2: 128 / 192 / 224 / 256)
+};
+// tma_ok: K % 128 == 0 and 16-byte aligned operands. force_bt: 0 = automatic, 32/64/128 pins the
+// single-CTA tile, 1000 + BT the CTA-pair tile. allow_pair = false when the device cannot
+// co-schedule the pair kernel.
+SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, int force_bt, bool allow_pair);
+
 // out (M,N_out) s32 = x (M,K) s8 x W24 (N_out,K)^T, W24 given as W_comp (N_out,K/2) + w_meta (N_out,K/32).
 // force_bt: 32/64/128 pins the token-tile width, anything else selects it automatically.
 int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,

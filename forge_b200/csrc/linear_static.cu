@@ -62,5 +62,6 @@ extern "C" int forge_int8_linear_static(const void* x, const int8_t* w_int8, con
     const int r = quantize_activation(static_cast<const __half*>(x), act_int8, act_scale, M, K, s);
     if (r != kOk) return r;
     return dense_gemm_dequant(act_int8, w_int8, act_scale, static_cast<const __half*>(w_scale),
-                              static_cast<const __half*>(bias), static_cast<__half*>(output), M, K, N, s, 0);
+                              static_cast<const __half*>(bias), static_cast<__half*>(output), M, K, N, s,
+                              tuning_knob(kKnobDenseTile));
 }

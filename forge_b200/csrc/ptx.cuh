@@ -368,6 +368,15 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
                  : "memory");
 }
 
+// The same arrival delivered to the barrier at this shared-memory offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void tc_commit_pair_mask(uint32_t bar_addr, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            bar_addr),
+        "h"(cta_mask)
+        : "memory");
+}
+
 __device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                              uint32_t accumulate) {
     asm volatile(
@@ -394,6 +403,11 @@ __device__ __forceinline__ void umma_i8_sp_pair(uint32_t tmem_d, uint64_t desc_a
 
 __device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// smem -> TMEM copy of 128 lanes x 256 bits (8 columns) in both CTAs of the pair.
+__device__ __forceinline__ void tmem_cp_128x256b_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
 }}  // namespace fb200::ptx

@@ -83,10 +83,12 @@ class QuantizedLinear(nn.Module, _ScratchMixin):
 
     @torch.no_grad()
     def quantize_weight(self, weight_fp):
-        if self.w_int8.is_cuda:   # one kernel on the module's device (IEEE arithmetic, = torch on the CPU)
+        if self.w_int8.is_cuda and weight_fp.shape[1] % 32 == 0:
+            # one kernel on the module's device (IEEE arithmetic: bit-identical to torch on the CPU)
             q, _, _, scale = _C.prepare_weight(weight_fp.detach().to(self.w_int8.device), sparse=False)
         else:
-            q, scale = quantize_weight_per_channel(weight_fp)
+            # any in_features, as the reference accepts (linear.py:167-173); the kernel walks 32-wide runs
+            q, scale = quantize_weight_per_channel(weight_fp.detach().to(self.w_int8.device))
         self.w_int8.copy_(q)
         self.w_scale.data.copy_(scale)
 

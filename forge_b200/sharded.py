@@ -61,16 +61,24 @@ def _forge_sparse_linear(x, w):
 
 def map_peer_buffers(tensor, group=None):
     """Maps `tensor` (same shape on every rank, one per GPU) into every process of `group`.
-    Returns (pointers, keepalive): pointers[r] is rank r's buffer as seen from this process.
-    Tries torch's symmetric memory first, then CUDA IPC through torch's storage sharing."""
+    Returns (pointers, keepalive, buffer): pointers[r] is rank r's buffer as seen from this process
+    and `buffer` is this rank's own tensor to use from now on (a fresh symmetric-memory allocation
+    when that route is taken). Tries torch's symmetric memory first, then CUDA IPC through torch's
+    storage sharing; the ranks agree on the route with one all-reduce, so that no rank enters a
+    collective the others skipped."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    buf = hdl = None
     try:
         import torch.distributed._symmetric_memory as symm_mem
         buf = symm_mem.empty(tensor.shape, dtype=tensor.dtype, device=tensor.device)
+        ok = 1
+    except Exception:   # no symmetric-memory support in this build / on this device
+        ok = 0
+    agreed = torch.tensor([ok], dtype=torch.int32, device=tensor.device)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+    if int(agreed.item()) == 1:
         hdl = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
         return [int(p) for p in hdl.buffer_ptrs], (buf, hdl), buf
-    except Exception:
-        pass
     info = tensor.untyped_storage()._share_cuda_()
     infos = [None] * world
     dist.all_gather_object(infos, info, group=group)
@@ -93,6 +101,12 @@ class ShardedSparseLinear:
     mode "columns": `weights` is the full weight; the constructor keeps only this rank's output
                     channels. forward(x) takes all tokens (replicated) and returns the full
                     (M, N) output on every rank.
+
+    With exchange="fused" the returned tensor is a view of a persistent buffer that the other ranks
+    write into: it is valid until the next forward() of this layer (clone it to keep it - a
+    residual connection or a saved activation must). The buffer is sized for the largest M seen so
+    far; smaller batches use its leading rows, so changing batch sizes does not redo the mapping.
+    exchange="nccl" returns a fresh tensor every call.
     """
 
     def __init__(self, weights, mode, group=None, chunks=4, local_linear=None, exchange="auto"):
@@ -108,7 +122,8 @@ class ShardedSparseLinear:
         self.exchange = exchange
         if exchange == "auto":
             self.exchange = "fused" if (local_linear is None and weights.W_comp.is_cuda) else "nccl"
-        self._peer = None   # (M, pointers, keepalive, out tensor, sync scalar)
+        self._peer = None   # (rows, pointers, keepalive, out tensor, sync scalar)
+        self._comm_stream = None
         self.N = weights.W_comp.shape[0]
         if mode == "columns":
             if self.N % self.world != 0:
@@ -131,31 +146,38 @@ class ShardedSparseLinear:
             return self._forward_fused(x)
         out = torch.empty((M, self.N), dtype=torch.float16, device=x.device)
         use_streams = x.is_cuda
-        comm_stream = torch.cuda.Stream() if use_streams else None
+        if use_streams and self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=x.device)
+        comm_stream = self._comm_stream
         pending = []
         for c in range(self.chunks):
             r0, rows = partition(M, self.chunks, c)
             if rows == 0:
                 continue
             y = self.local_linear(x[r0:r0 + rows], self.weights)          # (rows, n_local)
-            # concatenated along dim 0 by the collective; viewed as (rank, row, column) afterwards
-            flat = torch.empty((self.world * rows, n_local), dtype=torch.float16, device=x.device)
-            gathered = flat.view(self.world, rows, n_local)
             if use_streams:
                 ev = torch.cuda.Event()
                 ev.record()
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(ev)
+                    # allocated on the stream that uses it, so the caching allocator cannot hand the
+                    # block to the compute stream while the gather or the copy is still running
+                    flat = torch.empty((self.world * rows, n_local), dtype=torch.float16, device=x.device)
                     dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group)
-                    # interleave: out[r0+i, w*n_local + j] = gathered[w, i, j]
-                    out[r0:r0 + rows].view(rows, self.world, n_local).copy_(gathered.permute(1, 0, 2))
+                    # interleave: out[r0+i, w*n_local + j] = flat[w*rows + i, j]
+                    out[r0:r0 + rows].view(rows, self.world, n_local).copy_(
+                        flat.view(self.world, rows, n_local).permute(1, 0, 2))
                     done = torch.cuda.Event()
                     done.record()
                 y.record_stream(comm_stream)
+                out.record_stream(comm_stream)
                 pending.append(done)
             else:
+                # concatenated along dim 0 by the collective; viewed as (rank, row, column) afterwards
+                flat = torch.empty((self.world * rows, n_local), dtype=torch.float16, device=x.device)
                 dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group)
-                out[r0:r0 + rows].view(rows, self.world, n_local).copy_(gathered.permute(1, 0, 2))
+                out[r0:r0 + rows].view(rows, self.world, n_local).copy_(
+                    flat.view(self.world, rows, n_local).permute(1, 0, 2))
         for ev in pending:
             torch.cuda.current_stream().wait_event(ev)
         return out
@@ -169,11 +191,14 @@ class ShardedSparseLinear:
         from . import _lib
         M, K = x.shape
         n_local = self.N // self.world
-        if self._peer is None or self._peer[0] != M:
+        # every rank sees the same M (the activations are replicated), so all ranks re-map together
+        if self._peer is None or self._peer[0] < M:
+            self._peer = None   # drop the old mapping before making a larger one
             out = torch.empty((M, self.N), dtype=torch.float16, device=x.device)
             ptrs, keep, out = map_peer_buffers(out, self.group)
             self._peer = (M, ptrs, keep, out, torch.zeros(1, device=x.device))
         _, ptrs, _, out, token = self._peer
+        out = out[:M]
         xq, xs = C.fused_quantize_activation(x, M, K)
         col0_bytes = self.rank * n_local * 2
         arr = (ctypes.c_void_p * self.world)(*[p + col0_bytes for p in ptrs])

@@ -110,7 +110,14 @@ enum {
 };
 
 /* forge::gemm::sparse_int8_gemm_plan - include/forge/gemm/int8_sparse.cuh:33-50,
- * src/gemm/int8_sparse.cu:875-920. Writes the (tile, split_k) forge_sparse_int8_gemm will run. */
+ * src/gemm/int8_sparse.cu:875-920. Writes the (tile, split_k) forge_sparse_int8_gemm will run,
+ * chosen by the same routine the GEMM's own dispatch calls. split_k is always 1: the s32
+ * accumulator in tensor memory covers the whole K range. The tcgen05 tile set is reported through
+ * the reference's three ids: FORGE_SPARSE_TILE_256x128 = the CTA-pair kernel (256 weight rows x
+ * 224 tokens per pair of SMs), 128x128 = one CTA with 128 tokens, 128x64 = one CTA with 64 or -
+ * for M <= 32 - 32 tokens, and also the answer for shapes only the plain-CUDA kernel takes
+ * (K % 128 != 0; the plan sees no pointers and assumes 16-byte aligned operands). Passing the
+ * planned tile back to forge_sparse_int8_gemm runs exactly the kernel the automatic path runs. */
 int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_workspace, int tile, int* out_tile,
                                 int* out_split_k);
 
@@ -243,14 +250,21 @@ int forge_int8_conv_transpose2d_k2s2_forward(const void* input, const int8_t* we
 
 /* ---------------------------------------------------------------- diagnostics (additive) */
 
-/* Tuning/testing knobs: pin the dense tile width (64/128/256) or the sparse token-tile width
- * (32/64/128); 0 restores automatic selection. Process-wide. */
-void forge_b200_set_dense_tile(int bn);
-void forge_b200_set_sparse_tile(int bt);
-
-/* Reads (and, if reset != 0, clears) the device status word of the current device. 0 means no
- * kernel gave up on a wait; synchronises the device. */
+/* Every wait inside the tcgen05 kernels (on a TMA load, a tensor-core commit, a free pipeline
+ * stage) is bounded at two seconds. A wait that runs out makes the kernel record a code in a
+ * per-device status word and leave through its normal teardown, so the context stays usable; the
+ * output of that launch is then incomplete.
+ *
+ * forge_b200_device_status: FORGE_B200_OK when no kernel on the current device has given up since
+ * the last reset, FORGE_B200_DEVICE_TIMEOUT when one has (FORGE_B200_LAUNCH_FAILED when the word
+ * cannot be read). forge_b200_device_status_raw returns the recorded code itself:
+ *   100-104 dense GEMM, 200-204 2:4-sparse GEMM, 300-304 / 400-404 their CTA-pair forms,
+ *   500-506 fused quantize + sparse GEMM, 600-605 convolution; within a range x00 = misaligned
+ *   shared memory, x01 = producer waiting for a free stage, x02 = MMA issuer waiting for a drained
+ *   accumulator, x03 = MMA issuer waiting for operands, x04 and up = epilogue / gather waits.
+ * Both synchronise the device; reset != 0 clears the word after reading it. */
 int forge_b200_device_status(int reset);
+int forge_b200_device_status_raw(int reset);
 
 const char* forge_b200_status_string(int status);
 

@@ -18,7 +18,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libforge_ref.so")
-REFERENCE_ROOT = os.environ.get("FORGE_REFERENCE_ROOT", "/root/reference")
+# The reference source tree: $FORGE_REFERENCE_ROOT, else a directory named "reference" next to this
+# repository's checkout.
+REFERENCE_ROOT = os.environ.get("FORGE_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 REF_SOURCES = [
     "src/quant/quantize.cu", "src/quant/dequantize.cu",
     "src/sparsity/prune_compress.cu", "src/sparsity/pack_metadata.cu",
@@ -43,10 +45,14 @@ def build_oracle(force=False):
     return ORACLE_SO
 
 
+def reference_sources_present():
+    return all(os.path.exists(os.path.join(REFERENCE_ROOT, s)) for s in REF_SOURCES)
+
+
 def build_ref(force=False):
     """Returns the path of libforge_ref.so, or None when it is neither built nor buildable."""
     srcs = [os.path.join(REFERENCE_ROOT, s) for s in REF_SOURCES]
-    if not all(os.path.exists(s) for s in srcs):
+    if not reference_sources_present():
         return REF_SO if os.path.exists(REF_SO) else None
     shim = os.path.join(HERE, "ref_shim.cu")
     if force or _stale(REF_SO, srcs + [shim]):

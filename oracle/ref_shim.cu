@@ -3,6 +3,8 @@
 // TEST INFRASTRUCTURE: built by oracle/build.py into oracle/_ref/libforge_ref.so, only when
 // the reference source tree is present; loaded only by tests/ and bench.py's comparison legs.
 #include <forge/gemm/int8_dense.cuh>
+#include <forge/gemm/int8_dp4a.cuh>
+#include <forge/gemm/int8_gemm.cuh>
 #include <forge/gemm/int8_sparse.cuh>
 #include <forge/nn/int8_conv2d.cuh>
 #include <forge/nn/int8_conv_transpose2d.cuh>
@@ -50,6 +52,27 @@ void ref_sparse_int8_linear(const void* x, const int8_t* Wc, const uint32_t* met
     forge::gemm::sparse_int8_linear((const __half*)x, Wc, meta, (const __half*)ws, (const __half*)bias, (__half*)out,
                                     M, K, N, sx, ss, wksp, split_k, (cudaStream_t)stream, path);
 }
+void ref_splitk_reduce(const float* wksp, const void* bias, void* out, int M, int N, void* stream) {
+    forge::gemm::splitk_reduce(wksp, (const __half*)bias, (__half*)out, M, N, (cudaStream_t)stream);
+}
+// the dispatch front end and the legacy dp4a backend (src/gemm/int8_gemm.cu, src/gemm/int8_dp4a.cu)
+void ref_int8_gemm(const int8_t* A, const int8_t* B, const float* as, const void* ws, const void* bias, void* out,
+                   int M, int K, int N, void* stream) {
+    forge::gemm::int8_gemm(A, B, as, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N,
+                           (cudaStream_t)stream);
+}
+void ref_int8_dp4a_gemm_dequant(const int8_t* A, const int8_t* B, const float* as, const void* ws, const void* bias,
+                                void* out, int M, int K, int N, void* stream) {
+    forge::gemm::int8_dp4a_gemm_dequant(A, B, as, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N,
+                                        (cudaStream_t)stream);
+}
+void ref_int8_dp4a_linear(const void* x, const int8_t* w, const void* ws, const void* bias, void* out, int M, int K,
+                          int N, int8_t* sa, float* ss, void* stream) {
+    forge::gemm::int8_dp4a_linear((const __half*)x, w, (const __half*)ws, (const __half*)bias, (__half*)out, M, K, N,
+                                  sa, ss, (cudaStream_t)stream);
+}
+int ref_get_compute_capability(int device) { return forge::gemm::get_compute_capability(device); }
+int ref_has_wmma_int8(int device) { return forge::gemm::has_wmma_int8(device) ? 1 : 0; }
 void ref_prune_compress_24(const int8_t* w, int8_t* c, uint8_t* m, int N, int K, void* stream) {
     forge::sparsity::prune_compress_24(w, c, m, N, K, (cudaStream_t)stream);
 }

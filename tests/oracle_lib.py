@@ -187,6 +187,28 @@ def ref_available():
     return os.path.exists(REF_SO)
 
 
+def reference_sources_present():
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import build as oracle_build
+    return oracle_build.reference_sources_present()
+
+
+def require_ref():
+    """Gate of every comparison against the reference's own kernels. Returns when
+    oracle/_ref/libforge_ref.so is there. If it is missing although the reference sources are
+    present, the test FAILS (the checker was not built: run `python oracle/build.py`); if the
+    sources are absent too, the test is reported as skipped with the reason - never silently
+    passed without the reference."""
+    import pytest
+    if ref_available():
+        return True
+    if reference_sources_present():
+        pytest.fail("oracle/_ref/libforge_ref.so is not built although the reference sources are present; "
+                    "run `python oracle/build.py`")
+    pytest.skip("reference kernels unavailable: oracle/_ref/libforge_ref.so is not in this checkout and the "
+                "reference sources are not here to build it (the checks against the CPU oracle above did run)")
+
+
 def ref():
     global _ref
     if _ref is None:
@@ -208,6 +230,14 @@ def ref():
         lib.ref_int8_conv_transpose2d_k2s2_workspace_size.restype = ctypes.c_ulonglong
         lib.ref_int8_conv_transpose2d_k2s2_forward.argtypes = [_vp] * 5 + [_i] * 5 + [_vp, _vp]
         lib.ref_int8_conv_transpose2d_k2s2_forward.restype = None
+        lib.ref_splitk_reduce.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        lib.ref_int8_gemm.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        lib.ref_int8_dp4a_gemm_dequant.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        lib.ref_int8_dp4a_linear.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]
+        lib.ref_get_compute_capability.argtypes = [_i]
+        lib.ref_has_wmma_int8.argtypes = [_i]
+        for name in ("ref_splitk_reduce", "ref_int8_gemm", "ref_int8_dp4a_gemm_dequant", "ref_int8_dp4a_linear"):
+            getattr(lib, name).restype = None
         for name in ("ref_fused_quantize_activation", "ref_quantize_two_pass", "ref_fused_dequantize_bias",
                      "ref_int8_gemm_dequant", "ref_int8_linear", "ref_sparse_int8_gemm", "ref_sparse_int8_linear",
                      "ref_prune_compress_24", "ref_pack_metadata"):

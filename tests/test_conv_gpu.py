@@ -68,7 +68,7 @@ def _check_conv(N, C_in, H, W, C_out, k, p, s, d, use_bias, seed=42, weight_offs
     assert got.shape == expect.shape
     assert np.array_equal(got.view(np.uint16), expect.view(np.uint16)), \
         f"conv differs from the composed pipeline: {np.count_nonzero(got.view(np.uint16) != expect.view(np.uint16))}"
-    if O.ref_available() and _ref_workspace_aligned(expect.shape[2] * expect.shape[3], K):
+    if _ref_workspace_aligned(expect.shape[2] * expect.shape[3], K) and O.require_ref():
         # .clone(): the reference's 16-byte weight loads need an aligned matrix
         ref = O.ref_int8_conv2d(xd, wd.clone(), sd, bd, k[0], k[1], p[0], p[1], s[0], s[1], d[0], d[1])
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "conv differs from the reference pipeline"
@@ -157,7 +157,7 @@ def test_conv2d_non_finite_pixels_follow_the_quantizer():
     both_nan = np.isnan(got) & np.isnan(expect)
     assert both_nan.any() and not both_nan.all()
     assert np.array_equal(got.view(np.uint16)[~both_nan], expect.view(np.uint16)[~both_nan])
-    if O.ref_available():
+    if O.require_ref():
         ref = O.ref_int8_conv2d(x.to(DEV), w.to(DEV), w_scale.to(DEV), bias.to(DEV), 3, 3, 1, 1, 1, 1, 1, 1)
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
 
@@ -186,7 +186,7 @@ def test_workspace_sizes_match_reference_formulas():
     assert lib.forge_int8_conv2d_workspace_size(8, 16, 16, Co, 3, 3, 1, 1, 1, 1, 1, 1) == M * K * 3 + M * 4 + M * Co * 2
     assert lib.forge_int8_conv_transpose2d_k2s2_workspace_size(32, 16, 16, 64) == \
         256 * 32 * 3 + 256 * 4 + 256 * 2 + 256 * 256 * 2
-    if O.ref_available():
+    if O.require_ref():
         assert lib.forge_int8_conv2d_workspace_size(7, 32, 32, 16, 2, 2, 0, 0, 2, 2, 1, 1) == \
             O.ref().ref_int8_conv2d_workspace_size(7, 32, 32, 16, 2, 2, 0, 0, 2, 2, 1, 1)
 
@@ -209,7 +209,7 @@ def _check_conv_transpose(N, C_in, H, W, C_out, use_bias, seed=42):
     expect = O.conv_transpose_k2s2_scatter(gem, None if bias is None else bias.numpy(), N, H, W, C_out)
     got = out.cpu().numpy()
     assert np.array_equal(got.view(np.uint16), expect.view(np.uint16))
-    if O.ref_available() and _ref_workspace_aligned(H * W, C_in):
+    if _ref_workspace_aligned(H * W, C_in) and O.require_ref():
         ref = O.ref_int8_conv_transpose2d_k2s2(xd, wd, sd, bd)
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
 

@@ -61,7 +61,7 @@ def test_dequant_bit_exact(M, K, N, with_bias):
     want = O.dequantize_bias(acc, a_s.numpy(), w_s.numpy(), None if bias is None else bias.numpy(),
                              gemm_epilogue=True)
     assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
-    if O.ref_available():
+    if O.require_ref():
         ref = O.ref_int8_gemm_dequant(dA, dB, das, dws, dbias)
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "differs from the reference wmma kernel"
@@ -139,7 +139,7 @@ def test_int8_linear_matches_quantize_then_gemm():
     _status_ok()
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
     assert torch.equal(sa, q) and torch.equal(ss, s)
-    if O.ref_available():
+    if O.require_ref():
         ref = torch.empty_like(out)
         sa2, ss2 = torch.empty_like(sa), torch.empty_like(ss)
         dB, dws, dbias = B.to(DEV), w_s.to(DEV), bias.to(DEV)

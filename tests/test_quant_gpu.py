@@ -34,7 +34,7 @@ def test_quantize_matches_reference_kernel_and_oracle(M, K, offset):
     _, x = _make_x(M, K, offset, 42 + M + K)
     q, s = C.fused_quantize_activation(x, M, K)
     torch.cuda.synchronize()
-    if O.ref_available():
+    if O.require_ref():
         q_ref, s_ref = O.ref_quantize(x)
         q2_ref, s2_ref = O.ref_quantize(x, two_pass=True)
         torch.cuda.synchronize()
@@ -56,11 +56,48 @@ def test_quantize_zero_rows_and_outliers():
     x[6, 17] = 65504.0
     x = x.to(torch.float16).to(DEV)
     q, s = C.fused_quantize_activation(x, M, K)
-    if O.ref_available():
+    if O.require_ref():
         q_ref, s_ref = O.ref_quantize(x)
         assert torch.equal(q, q_ref) and torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
     assert int(q[5].abs().max()) == 0
     assert q.abs().max() <= 127 or q.min() >= -128
+
+
+@pytest.mark.parametrize("K", [256, 100, 4096, 14336])
+def test_quantize_non_finite_inputs(K):
+    """+-Inf and NaN activations (overflowed FP16 upstream). The reference's arithmetic gives: NaN is
+    skipped by the row maximum (max.ftz returns the other operand) and quantizes to 0; a row holding
+    an infinity gets scale = inf, reciprocal 0, and every value - the infinity included, inf * 0 = NaN
+    -> 0 - quantizes to 0 (src/quant/quantize.cu:48-58,112-130). Both kernels of this library must
+    reproduce the reference kernels bit for bit, including the scales."""
+    M = 12
+    g = torch.Generator().manual_seed(K)
+    x = (torch.randn((M, K), generator=g) * 2).to(torch.float16)
+    inf, nan = float("inf"), float("nan")
+    x[1, 3] = inf
+    x[2, K - 1] = -inf
+    x[3, 0] = nan
+    x[4, 5], x[4, 6] = nan, inf
+    x[5, :] = nan
+    x[6, ::2] = nan
+    x[7, 1], x[7, 2] = inf, -inf
+    x[8, K // 2] = 65504.0
+    xd = x.to(DEV)
+    q, s = C.fused_quantize_activation(xd, M, K)
+    torch.cuda.synchronize()
+    qc, sc = q.cpu(), s.cpu()
+    for r in (1, 2, 4, 7):                                  # rows with an infinity
+        assert torch.isinf(sc[r]) and int(qc[r].abs().max()) == 0
+    assert int(qc[3, 0]) == 0 and torch.isfinite(sc[3]) and int(qc[3].abs().max()) == 127
+    assert int(qc[5].abs().max()) == 0 and float(sc[5]) == pytest.approx(1e-8 / 127.0, rel=1e-6)
+    assert int(qc[6, ::2].abs().max()) == 0 and int(qc[6].abs().max()) == 127
+    assert int(qc[8].abs().max()) == 127 and int(qc[0].abs().max()) == 127
+    if O.require_ref():
+        for two_pass in (False, True):
+            q_ref, s_ref = O.ref_quantize(xd, two_pass=two_pass)
+            torch.cuda.synchronize()
+            assert torch.equal(q, q_ref), f"values differ from the reference kernel (two_pass={two_pass})"
+            assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
 
 
 def test_public_two_pass_kernel_path_is_bit_identical():
@@ -89,7 +126,7 @@ def test_dequantize_bias_bit_exact(M, N, with_bias):
     d = [t.to(DEV) if t is not None else None for t in (acc, a_s, w_s, bias)]
     out = C.fused_dequantize_bias(d[0], d[1], d[2], d[3], M, N)
     torch.cuda.synchronize()
-    if O.ref_available():
+    if O.require_ref():
         out_ref = O.ref_dequantize_bias(*d)
         assert torch.equal(out.view(torch.int16), out_ref.view(torch.int16))
     if M * N <= 1 << 22:

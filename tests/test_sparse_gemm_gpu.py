@@ -73,7 +73,7 @@ def test_dequant_bit_exact_every_tile(M, K, N, tile):
     acc = O.sparse_gemm_s32(comp.cpu().numpy(), x.numpy(), packed.cpu().numpy().view(np.uint32))
     want = O.dequantize_bias(acc, a_s.numpy(), w_s.numpy(), bias.numpy() if use_bias else None, gemm_epilogue=True)
     assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
-    if O.ref_available():
+    if O.require_ref():
         ref = O.ref_sparse_int8_gemm(comp, dx, packed, das, dws, dbias)
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "differs from the reference mma.sp kernel"

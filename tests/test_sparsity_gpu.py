@@ -39,7 +39,7 @@ def test_prune_compress_pack_exact(N, K):
     if K % 32 == 0:
         packed_cpu = O.pack_metadata(raw_cpu, N, K)
         assert np.array_equal(packed.cpu().numpy().view(np.uint32), packed_cpu)
-    if O.ref_available() and K % 32 == 0:
+    if K % 32 == 0 and O.require_ref():
         comp_r, raw_r, packed_r = O.ref_prune_pack(w.to(DEV))
         assert torch.equal(comp, comp_r) and torch.equal(raw, raw_r) and torch.equal(packed, packed_r)
 
@@ -61,7 +61,7 @@ def test_prune_every_order_and_tie_pattern():
         comp_cpu, raw_cpu = O.prune_compress_24(w.numpy())
         assert np.array_equal(comp.cpu().numpy(), comp_cpu)
         assert np.array_equal(raw.cpu().numpy(), raw_cpu)
-        if O.ref_available() and K % 32 == 0:
+        if K % 32 == 0 and O.require_ref():
             comp_r, raw_r, _ = O.ref_prune_pack(w.to(DEV))
             assert torch.equal(comp, comp_r) and torch.equal(raw, raw_r)
     # the scalar kernel (misaligned compressed output)

@@ -10,9 +10,11 @@ second call must not see anything the first left in the shared array), and requi
 to equal forge_int8_linear's bit for bit - the same tolerance the other GEMM tests use. It also
 checks that over-sized requests are refused. The file sorts last so that a run that stops at the
 first failure has already executed every other test."""
+import numpy as np
 import pytest
 import torch
 
+import oracle_lib as O
 from forge_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -55,6 +57,33 @@ def test_static_scratch_linear_matches_int8_linear_twice_in_a_row():
         torch.cuda.synchronize()
         assert lib.forge_b200_device_status(1) == 0
         assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+def test_static_scratch_linear_against_the_cpu_oracle():
+    """Independent of forge_int8_linear: the CPU oracle's chain on the same input. The quantized
+    values never leave the library here, so the oracle's own quantizer is used; it may differ from
+    the GPU's by one int8 step where x / scale falls next to a rounding boundary (IEEE divide against
+    the kernels' approximate one), which moves an output by at most (sum of |w|) * scales."""
+    lib = _lib.load()
+    M, K, N = 96, 512, 160
+    x, w, w_s, bias = _case(M, K, N, 4)
+    out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    st = lib.forge_int8_linear_static(x.data_ptr(), w.data_ptr(), w_s.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                      M, K, N, torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert lib.forge_b200_device_status(1) == 0
+    q, s = O.quantize(x.cpu().numpy())
+    want = O.dequantize_bias(O.gemm_s32(q, w.cpu().numpy()), s, w_s.cpu().numpy(), bias.cpu().numpy(),
+                             gemm_epilogue=True).astype(np.float32)
+    got = out.cpu().numpy().astype(np.float32)
+    # bound of one flipped int8 step per activation element: |w|_1 * act_scale * w_scale (+ fp16 rounding)
+    slack = (np.abs(w.cpu().numpy().astype(np.float32)).sum(axis=1)[None, :] * s[:, None] *
+             w_s.cpu().numpy().astype(np.float32)[None, :])
+    assert np.all(np.abs(got - want) <= slack + 2e-3 * np.abs(want) + 1e-3)
+    # and in practice almost every output is identical
+    assert np.mean(out.cpu().numpy().view(np.uint16) == O.dequantize_bias(
+        O.gemm_s32(q, w.cpu().numpy()), s, w_s.cpu().numpy(), bias.cpu().numpy(), gemm_epilogue=True).view(np.uint16)) > 0.9
 
 
 def test_static_scratch_linear_rejects_oversized_requests():
