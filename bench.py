@@ -111,7 +111,7 @@ class ClockSampler(threading.Thread):
                     for bit, name in names.items():
                         if r & bit:
                             self.reasons.add(name)
-                time.sleep(0.02)
+                time.sleep(0.002 if self.active.is_set() else 0.02)
         except Exception as e:  # clocks are evidence, not the product: report the failure, keep benchmarking
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
@@ -188,6 +188,39 @@ def _median_ms(fn, steps, warmup, flush=None):
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
     return statistics.median(times)
+
+
+def _ceilings(lib, dev, sm_mhz):
+    """The two rates that bound the GEMM kernels, measured on this GPU by the library's built-in probes:
+    clocks per tcgen05.mma kind::i8 instruction with operands resident in shared memory (dense and
+    2:4-sparse, in the tile shapes the pair kernels use, with their one commit per four instructions), and
+    the bytes per clock one SM receives from L2 through TMA when every SM pulls at once. TOP/s figures are
+    at `sm_mhz` (the clock sampled during the timed region)."""
+    import torch
+    n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    out = {}
+    try:
+        dense = lib.forge_b200_probe_mma_rate(1, 256, 0, 1, n_sms)
+        sparse = lib.forge_b200_probe_mma_rate(1, 224, 1, 1, n_sms)
+        out["dense_pair_n256_clocks_per_mma"] = dense
+        out["sparse_pair_n224_clocks_per_mma"] = sparse
+        out["dense_ops_per_clock_per_sm"] = 2.0 * 128 * 256 * 32 / dense
+        out["sparse_dense_equiv_ops_per_clock_per_sm"] = 2.0 * 128 * 224 * 64 / sparse
+        buf = torch.randint(-127, 128, (8192, 4096), dtype=torch.int8, device=dev)   # 32 MB: L2 resident
+        out["tma_ingest_bytes_per_clock_one_sm"] = lib.forge_b200_probe_tma_ingest(buf.data_ptr(), 8192, 4096, 4, 1)
+        out["tma_ingest_bytes_per_clock_per_sm_all_sms"] = lib.forge_b200_probe_tma_ingest(buf.data_ptr(), 8192, 4096,
+                                                                                           4, n_sms)
+        if sm_mhz:
+            out["dense_tensor_ceiling_tops_at_sampled_clock"] = out["dense_ops_per_clock_per_sm"] * n_sms * sm_mhz * 1e6 / 1e12
+            out["sparse_tensor_ceiling_tops_at_sampled_clock"] = (out["sparse_dense_equiv_ops_per_clock_per_sm"] * n_sms *
+                                                                 sm_mhz * 1e6 / 1e12)
+            out["l2_to_sm_TBps_at_sampled_clock"] = (out["tma_ingest_bytes_per_clock_per_sm_all_sms"] * n_sms * sm_mhz *
+                                                     1e6 / 1e12)
+        if lib.forge_b200_device_status(1) != 0:
+            out["error"] = "a probe gave up on a bounded wait"
+    except Exception as e:
+        out["error"] = f"{type(e).__name__}: {e}"
+    return out
 
 
 def _single_gpu_extras(lib, dev, peaks):
@@ -373,6 +406,7 @@ def run_b200(args):
 
     peaks = _peaks()
     extras = _single_gpu_extras(lib, dev, peaks) if rank == 0 else None
+    ceilings = _ceilings(lib, dev, clocks["sm_mhz"]) if rank == 0 else None
     sharded = None
     if world > 1:
         barrier()
@@ -395,6 +429,9 @@ def run_b200(args):
         "peak_basis": f"2 x {'sustained' if sustained_region else 'burst'} cuBLAS bf16 TFLOP/s of {peaks['source']} "
                       "(kind::i8 issues at twice the bf16 rate); nominal dense int8 is 4500",
         "frac_of_nominal_4500": achieved / NOMINAL_DENSE_TOPS,
+        # the tensor pipe's own rate on this GPU (built-in probe) at the clock sampled during the timed region
+        "frac_of_measured_tensor_ceiling": (achieved / ceilings["dense_tensor_ceiling_tops_at_sampled_clock"])
+        if ceilings and ceilings.get("dense_tensor_ceiling_tops_at_sampled_clock") else None,
     }
     sus_tops = OPS_PER_STEP * sus_steps / (sus_ms * 1e-3) / 1e12
     sustained = {
@@ -429,6 +466,7 @@ def run_b200(args):
         "sustained": sustained,
         "cpu_baseline": cpu,
         "extras": extras,
+        "ceilings": ceilings,
         "sharded": sharded,
     }))
     if world > 1:
@@ -664,7 +702,8 @@ def run_case(args):
                       "unit": unit,
                       "bound": bound, "peak": peak, "frac": achieved / peak, "peak_source": peaks["source"],
                       "l2_flush_between_launches": bool(args.flush_l2), "steps": args.steps, "tile": args.tile, "reps": args.reps * reps_in_fn, "cuda_graph": bool(args.graph),
-                      "rotating_operand_sets": len(fns), "knobs": args.knob, "probe": probe}))
+                      "rotating_operand_sets": len(fns), "knobs": args.knob, "probe": probe,
+                      "cta_pairs": lib.forge_b200_get_tuning(4)}))
 
 
 def _init_ranks(timeout_s=300):
@@ -907,6 +946,30 @@ def main():
         if args.steps == 1000:
             args.steps = 50
         run_sharded_mlp(args)
+        return
+    if args.case == "probe":
+        import torch
+        from forge_b200 import _lib
+        torch.cuda.set_device(0)
+        lib = _lib.load()
+        dev = torch.device("cuda", 0)
+        n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        rows = {}
+        for pair in (1, 0):
+            for sparse in (0, 1):
+                for n in (64, 128, 192, 224, 256):
+                    for commits in (0, 1, 2):
+                        if commits == 2 and not pair:
+                            continue
+                        key = f"{'pair M=256' if pair else 'one CTA M=128'} {'sparse K=64' if sparse else 'dense K=32'} N={n} commits={commits}"
+                        rows[key] = lib.forge_b200_probe_mma_rate(pair, n, sparse, commits, n_sms)
+        buf = torch.randint(-127, 128, (8192, 4096), dtype=torch.int8, device=dev)
+        for producers in (1, 2, 4):
+            for ctas in (1, n_sms // 2, n_sms):
+                rows[f"tma ingest B/clk/SM producers={producers} ctas={ctas}"] = lib.forge_b200_probe_tma_ingest(
+                    buf.data_ptr(), 8192, 4096, producers, ctas)
+        print(json.dumps({"case": "probe", "sms": n_sms, "clocks_per_mma_and_bytes_per_clock": rows,
+                          "status": lib.forge_b200_device_status(1)}))
         return
     if args.case != "headline":
         run_case(args)

@@ -57,6 +57,8 @@ INTERNAL_SIGNATURES = {
     "forge_b200_get_tuning": [_i],
     "forge_b200_selftest_wait_timeout": [ctypes.c_uint, _vp],
     "forge_b200_read_probe": [_vp, _i],
+    "forge_b200_probe_mma_rate": [_i, _i, _i, _i, _i],
+    "forge_b200_probe_tma_ingest": [_vp, _i, _i, _i, _i],
 }
 _VOID_RETURN = {"forge_b200_set_dense_tile", "forge_b200_set_sparse_tile", "forge_b200_set_tuning"}
 
@@ -84,6 +86,8 @@ def load():
             fn.restype = None
         elif name == "forge_b200_status_string":
             fn.restype = ctypes.c_char_p
+        elif name.startswith("forge_b200_probe_"):
+            fn.restype = ctypes.c_double
         elif name in ("forge_w8a8_gated_mlp_workspace_bytes", "forge_int8_conv2d_workspace_size",
                       "forge_int8_conv_transpose2d_k2s2_workspace_size"):
             fn.restype = ctypes.c_ulonglong

@@ -21,12 +21,13 @@ inline __half* H(void* p) { return static_cast<__half*>(p); }
 
 // Tile id of the reference API -> tile knob of the tcgen05 kernels: the reference's 256-row
 // weight tile is the CTA-pair kernel (256 weight rows x 224 tokens per pair, knob 1000 + 224);
-// its 128-row tiles are the single-CTA kernel with 128 tokens, or 64 (32 when M <= 32) tokens.
+// its 128-row tiles are the single-CTA kernel with 128 tokens, or 64 (32 when M <= 32) tokens; for
+// 1-2 tokens the smallest id leaves the choice automatic (the weight-streaming kernel).
 inline int tile_to_bt(int tile, int M) {
     switch (tile) {
     case FORGE_SPARSE_TILE_256x128: return 1224;
     case FORGE_SPARSE_TILE_128x128: return 128;
-    case FORGE_SPARSE_TILE_128x64: return M <= 32 ? 32 : 64;
+    case FORGE_SPARSE_TILE_128x64: return M <= 2 ? 0 : (M <= 32 ? 32 : 64);   // 1-2 tokens: the streaming kernel
     default: return 0;
     }
 }
@@ -114,7 +115,7 @@ int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_w
     if (tile >= FORGE_SPARSE_NUM_TILES) tile = FORGE_SPARSE_TILE_AUTO;   // reference: int8_sparse.cu:895
     int bt = force_sparse_bt();
     if (bt == 0 && tile >= 0) bt = tile_to_bt(tile, M);
-    const SparseChoice c = sparse_choose(M, K, N_out, K % 128 == 0, bt, true);
+    const SparseChoice c = sparse_choose(M, K, N_out, K % 128 == 0, K % 32 == 0, bt, true);
     if (out_tile) *out_tile = choice_to_tile(c);
     if (out_split_k) *out_split_k = 1;
     return kOk;

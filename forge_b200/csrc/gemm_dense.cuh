@@ -33,8 +33,13 @@ enum TuningKnob : int {
     kKnobMaxPairs = 2,         // CTA-pair kernels: launch at most this many pairs
     kKnobPairFlags = 3,        // CTA-pair kernels, measurement only: bit 0 = operands stay resident after the
                                // first ring fill (wrong results; tensor-core side alone), bit 1 = one commit
-                               // per CTA to free a stage, bit 2 = sparse MMA thread records its wait clocks
+                               // per CTA to free a stage, bit 2 = sparse MMA thread records its wait clocks,
+                               // bit 3 = dense: no half tiles in the last wave
+    kKnobLastPairs = 4,        // written by the launcher: CTA pairs of the last pair-kernel launch
+    kKnobGemvVariant = 5,      // 1-4 token sparse kernel: 1 = token slices in registers, 2 = in shared memory
+    kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)
 };
 int tuning_knob(int key);
+void set_tuning_knob(int key, int value);
 
 }  // namespace fb200

@@ -99,6 +99,7 @@ constexpr int kFlagResident = 1;    // stop loading after the first ring fill: t
 constexpr int kFlagTwoCommits = 2;  // free a stage with one tcgen05.commit per CTA instead of one commit
                                     // delivered to both CTAs' barriers
 constexpr int kFlagProbe = 4;       // sparse: pair 0's MMA thread records where its clocks go (g_pair_probe)
+constexpr int kFlagNoSplit = 8;     // dense: never cut the last wave's tiles in halves
 
 // kFlagProbe: [0] total clocks of the MMA thread's loop, [1] waiting for operands, [2] waiting for a
 // drained accumulator, [3] stages, [4] tiles
@@ -119,6 +120,41 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int a_blocks, int b_block
     c.a_blk = first + r % rows;
     c.b_blk = r / rows;
     return c;
+}
+
+// Work items of the dense pair kernel. The tiles are 256 x 256; when the last wave would leave more
+// than half of the pairs idle (0 < tiles % pairs <= pairs / 2), the tiles of that wave are cut into
+// two 256 x 128 halves so that the wave takes half as long (4096^3 on 74 pairs: 3.46 -> 3.5 waves
+// instead of 4).
+struct DenseWork {
+    int full;     // items [0, full) are whole tiles
+    int items;    // items [full, items) are halves of tiles full + (i - full) / 2
+};
+__host__ __device__ inline DenseWork dense_work(int tiles, int pairs, bool allow_split) {
+    DenseWork w;
+    const int rem = tiles % pairs;
+    const bool split = allow_split && tiles > pairs && rem > 0 && 2 * rem <= pairs;
+    w.full = split ? tiles - rem : tiles;
+    w.items = split ? tiles + rem : tiles;
+    return w;
+}
+struct DenseItem {
+    int tile;
+    int n_off;    // first column inside the tile (0 or 128)
+    int n_cols;   // 256 or 128
+};
+__device__ __forceinline__ DenseItem dense_item(int i, const DenseWork& w) {
+    DenseItem it;
+    if (i < w.full) {
+        it.tile = i;
+        it.n_off = 0;
+        it.n_cols = 256;
+    } else {
+        it.tile = w.full + ((i - w.full) >> 1);
+        it.n_off = ((i - w.full) & 1) * 128;
+        it.n_cols = 128;
+    }
+    return it;
 }
 
 // ============================================================================================
@@ -143,7 +179,8 @@ struct DensePairCfg {
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const __grid_constant__ CUtensorMap tm_c, const float* __restrict__ act_scale,
+                  const __grid_constant__ CUtensorMap tm_b_half, const __grid_constant__ CUtensorMap tm_c,
+                  const float* __restrict__ act_scale,
                   const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
                   int* __restrict__ status, int flags) {
     using Cfg = DensePairCfg;
@@ -166,10 +203,11 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
     const int m_blocks = (M + 255) / 256;
     const int n_blocks = (N + 255) / 256;
-    const int num_tiles = m_blocks * n_blocks;
     const int num_kb = (K + 127) / 128;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    const DenseWork work = dense_work(m_blocks * n_blocks, num_pairs, (flags & kFlagNoSplit) == 0);
+    const int num_tiles = work.items;   // work items: whole tiles, then halves of the last wave's tiles
 
     if (threadIdx.x == 0) init_bars(bars, Cfg::kStages, kEpiWarps);
     if (warp_id == 0 && lane == 0) {
@@ -198,7 +236,9 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             bool ok = true;
             int it = 0;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-                const TileCoord tc = tile_coord(t, m_blocks, n_blocks, kDenseBand);
+                const DenseItem item = dense_item(t, work);
+                const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, kDenseBand);
+                const bool half = item.n_cols == 128;
                 for (int kb = 0; kb < num_kb; kb++, it++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
                         atomicExch(status, 301);
@@ -211,8 +251,13 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     if ((flags & kFlagResident) != 0 && it >= Cfg::kStages) {
                         if (leader && !second) mbar_arrive(&bars.full[stage]);
                     } else if (!second) {
-                        if (leader) mbar_expect_tx(&bars.full[stage], 2 * Cfg::kStageBytes);
+                        if (leader)
+                            mbar_expect_tx(&bars.full[stage], 2 * (Cfg::kABytes + (half ? Cfg::kBBytes / 2 : Cfg::kBBytes)));
                         tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
+                    } else if (half) {
+                        // each CTA stages 64 of the 128 B rows of a half tile
+                        tma_load_2d_pair(sb, &tm_b_half, full_leader, kb * 128,
+                                         tc.b_blk * 256 + item.n_off + (int)rank * 64);
                     } else {
                         tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
                     }
@@ -226,12 +271,14 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     } else if (warp_id == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (leader && lane == 0) {
-            constexpr uint32_t idesc = make_idesc_i8(256, BN, false);
+            constexpr uint32_t idesc_full = make_idesc_i8(256, BN, false);
+            constexpr uint32_t idesc_half = make_idesc_i8(256, BN / 2, false);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs, local++) {
+                const uint32_t idesc = dense_item(t, work).n_cols == 128 ? idesc_half : idesc_full;
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 if (!mbar_wait(&bars.tmem_empty[buf], acc_phase ^ 1, bars.abort_flag)) {
@@ -285,12 +332,13 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         int sbuf = 0;
         bool ok = true;
         for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
-            const TileCoord tc = tile_coord(t, m_blocks, n_blocks, kDenseBand);
+            const DenseItem item = dense_item(t, work);
+            const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, kDenseBand);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row0 = tc.a_blk * 256 + (int)rank * 128;
             const int row = row0 + q * 32 + lane;
-            const int n0 = tc.b_blk * BN;
+            const int n0 = tc.b_blk * BN + item.n_off;
             __half* s_ws = smem_scale + buf * 2 * BN;
             __half* s_bias = s_ws + BN;
             float as = 0.f;
@@ -313,7 +361,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / CH; c++) {
+            for (int c = 0; c < item.n_cols / CH; c++) {
                 uint32_t packed[32];
                 if (EPI == 0) {
                     tmem_ld_32x32b_x32(taddr + c * CH, packed);
@@ -814,6 +862,7 @@ int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaSt
     int pairs = (int)std::min<long long>(tiles, max_pairs);
     const int cap = tuning_knob(kKnobMaxPairs);
     if (cap > 0 && cap < pairs) pairs = cap;
+    set_tuning_knob(kKnobLastPairs, pairs);
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
     return e == cudaSuccess ? kOk : kLaunchFailed;
@@ -823,7 +872,7 @@ template <int EPI>
 int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                       const __half* bias, void* out, int M, int K, int N, cudaStream_t stream) {
     static int max_pairs[64] = {};
-    CUtensorMap tm_a, tm_b, tm_c;
+    CUtensorMap tm_a, tm_b, tm_b_half, tm_c;
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         const uint64_t str[1] = {(uint64_t)K};
@@ -839,6 +888,13 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
             return kLaunchFailed;
     }
     {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+        const uint64_t str[1] = {(uint64_t)K};
+        const uint32_t box[2] = {128, 64};
+        if (!make_tmap(&tm_b_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return kLaunchFailed;
+    }
+    {
         const uint64_t esz = (EPI == 0) ? 4 : 2;
         const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
         const uint64_t str[1] = {(uint64_t)N * esz};
@@ -849,7 +905,8 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-    return launch_pairs(dense_pair_kernel<EPI>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b, tm_c,
+    return launch_pairs(dense_pair_kernel<EPI>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b,
+                        tm_b_half, tm_c,
                         act_scale, w_scale, bias, M, N, K, status, tuning_knob(kKnobPairFlags));
 }
 

@@ -13,11 +13,13 @@
 //              128B swizzle), activations (two 128-byte-wide swizzled atoms of BT rows) and the
 //              metadata slab (128 rows x 32 bytes, fetched as two 16-byte columns so that it
 //              lands as unswizzled 8-row x 16-byte core matrices).
-//   warp 1   : MMA issuer. tcgen05.cp moves the metadata into TMEM - the public w_meta layout
-//              (row-major uint32, nibble g at bits [4g,4g+4)) is already what the tensor core
-//              expects per lane: 2 columns per 64-deep step - then four
-//              tcgen05.mma.sp kind::i8 (M=128, N=BT, K=64) per slab.
-//   warps 2-5: epilogue. tcgen05.ld (lane = weight row, registers = tokens), dequantise, and
+//   warp 1   : MMA issuer: four tcgen05.mma.sp kind::i8 (M=128, N=BT, K=64) per slab.
+//   last warp: metadata copies. One tcgen05.cp per slab moves the metadata into TMEM as soon as it
+//              has landed (its own barrier) - the public w_meta layout (row-major uint32, nibble g
+//              at bits [4g,4g+4)) is already what the tensor core expects per lane: 2 columns per
+//              64-deep step. Issued from the MMA thread the copies sit in the MMA stream and cost
+//              about a fifth of a compute-bound kernel's time.
+//   warps 2-9: epilogue. tcgen05.ld (lane = weight row, registers = tokens), dequantise, and
 //              store straight to global memory: for one token the 32 lanes of a warp hold 32
 //              consecutive output columns, so every warp store is one contiguous segment.
 #include "common.cuh"
@@ -36,7 +38,7 @@ namespace {
 constexpr int BW = 128;          // weight rows per tile (UMMA M)
 constexpr int SLAB_K = 256;      // logical K per pipeline stage
 constexpr int kEpiWarps = 8;             // two warps per TMEM lane quarter, alternating 32-token chunks
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kThreads = 96 + 32 * kEpiWarps;   // TMA, MMA, epilogue warps, metadata-copy warp
 constexpr int kMetaBytes = BW * 32;        // 128 rows x 32 bytes per slab
 
 constexpr int kXbufBytes = 4 * 32 * 32 * (int)sizeof(float);   // gated epilogue: 4 warp pairs x 4 KB
@@ -47,7 +49,7 @@ struct SparseCfg {
     static constexpr int kBAtomBytes = BT * 128;
     static constexpr int kStageBytes = kABytes + 2 * kBAtomBytes + kMetaBytes;
     static constexpr int kAccBufs = (2 * BT + 32 <= 512) ? 2 : 1;
-    static constexpr int kBarBytes = 256;
+    static constexpr int kBarBytes = 320;   // up to 8 stages x 4 barriers + 4 accumulator barriers + 2 words
     static constexpr int kFixed = kBarBytes + (EPI == 2 ? kXbufBytes : 0);
     static constexpr int kStagesMax = (232448 - kFixed) / kStageBytes;
     static constexpr int kStages = kStagesMax > 8 ? 8 : kStagesMax;
@@ -104,7 +106,9 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     uint64_t* empty_bar = bars + Cfg::kStages;
     uint64_t* tmem_full = bars + 2 * Cfg::kStages;
     uint64_t* tmem_empty = tmem_full + 2;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint64_t* meta_full = tmem_empty + 2;                 // the stage's metadata slab has landed
+    uint64_t* meta_ready = meta_full + Cfg::kStages;      // ... is in tensor memory and the operands have landed
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(meta_ready + Cfg::kStages);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp_id = threadIdx.x >> 5;
@@ -124,6 +128,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int s = 0; s < Cfg::kStages; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+            mbar_init(&meta_full[s], 1);
+            mbar_init(&meta_ready[s], 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
@@ -164,20 +170,21 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
                     uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
-                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    mbar_expect_tx(&meta_full[stage], kMetaBytes);
+                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes - kMetaBytes);
                     if (EPI == 2) {
                         // 64 gate rows then 64 up rows; metadata per 16-byte column: [gate 64 rows][up 64 rows]
                         const int w_row = tc.w_blk * TILE_W;
-                        tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), w_row);
-                        tma_load_2d(sa + Cfg::kABytes / 2, &tm_w2, &full_bar[stage], kb * (SLAB_K / 2), w_row);
 #pragma unroll
                         for (int c = 0; c < 2; c++) {
-                            tma_load_3d(sm + c * 2048, &tm_meta, &full_bar[stage], 0, w_row, kb * 2 + c);
-                            tma_load_3d(sm + c * 2048 + 1024, &tm_meta2, &full_bar[stage], 0, w_row, kb * 2 + c);
+                            tma_load_3d(sm + c * 2048, &tm_meta, &meta_full[stage], 0, w_row, kb * 2 + c);
+                            tma_load_3d(sm + c * 2048 + 1024, &tm_meta2, &meta_full[stage], 0, w_row, kb * 2 + c);
                         }
+                        tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), w_row);
+                        tma_load_2d(sa + Cfg::kABytes / 2, &tm_w2, &full_bar[stage], kb * (SLAB_K / 2), w_row);
                     } else {
+                        tma_load_3d(sm, &tm_meta, &meta_full[stage], 0, tc.w_blk * BW, kb * 2);
                         tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), tc.w_blk * BW);
-                        tma_load_3d(sm, &tm_meta, &full_bar[stage], 0, tc.w_blk * BW, kb * 2);
                     }
                     tma_load_2d(sb, &tm_x, &full_bar[stage], kb * SLAB_K, tc.t_blk * BT);
                     tma_load_2d(sb + Cfg::kBAtomBytes, &tm_x, &full_bar[stage], kb * SLAB_K + 128, tc.t_blk * BT);
@@ -207,7 +214,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + buf * BT;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                    // meta_ready[s]: the slab's metadata is in tensor memory and its operands have landed
+                    if (!mbar_wait(&meta_ready[stage], phase, abort_flag)) {
                         atomicExch(status, 203);
                         ok = false;
                         break;
@@ -215,13 +223,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_stage + stage * Cfg::kStageBytes);
                     const uint32_t sb = sa + Cfg::kABytes;
-                    const uint32_t sm = sb + 2 * Cfg::kBAtomBytes;
                     const uint32_t te = tmem_meta + 8 * stage;
-                    // metadata: two 16-byte columns of 128 rows -> 2 x 4 TMEM columns. (Copying it one
-                    // slab ahead of its MMAs was measured and is slower: the wait for the next stage
-                    // then delays MMAs whose operands are already resident.)
-                    tmem_cp_128x128b(te, make_desc_noswizzle(sm, 2048, 128));
-                    tmem_cp_128x128b(te + 4, make_desc_noswizzle(sm + 2048, 2048, 128));
                     const uint64_t desc_a = make_desc_sw128(sa);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -236,6 +238,37 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     }
                 }
                 if (ok) tc_commit(&tmem_full[buf]);
+            }
+        }
+    } else if (warp_id == kThreads / 32 - 1) {
+        // ------------------------------------------------------------------ metadata copies
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(&meta_full[stage], phase, abort_flag)) {
+                        atomicExch(status, 205);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sm = smem_u32(smem_stage + stage * Cfg::kStageBytes) + Cfg::kABytes +
+                                        2 * Cfg::kBAtomBytes;
+                    // two 16-byte columns of 128 rows -> 8 TMEM columns
+                    tmem_cp_128x256b(tmem_meta + 8 * stage, make_desc_noswizzle(sm, 2048, 128));
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        atomicExch(status, 206);
+                        ok = false;
+                        break;
+                    }
+                    tc_commit(&meta_ready[stage]);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
             }
         }
     } else {
@@ -435,21 +468,24 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
     if (W_comp == nullptr || x == nullptr || w_meta == nullptr || out == nullptr) return kBadPointer;
     if (EPI == 1 && (act_scale == nullptr || w_scale == nullptr)) return kBadPointer;
     if (!device_is_sm100()) return kUnsupportedArch;
-    const bool tma_ok = (K % 128 == 0) && aligned16(W_comp) && aligned16(x) && aligned16(w_meta);
-    if (!tma_ok) {
+    const bool aligned = aligned16(W_comp) && aligned16(x) && aligned16(w_meta);
+    const bool tma_ok = (K % 128 == 0) && aligned;
+    SparseChoice c = sparse_choose(M, K, N_out, tma_ok, aligned, force_bt, true);
+    if (c.kind == 3)
+        return sparse_gemv(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream, EPI);
+    if (c.kind == 0) {
         const long long total = (long long)M * N_out;
         sparse_gemm_ragged_kernel<EPI><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
             W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
     }
-    SparseChoice c = sparse_choose(M, K, N_out, true, force_bt, true);
     if (c.kind == 2) {
         const int r = (EPI == 0) ? sparse_pair_s32(W_comp, x, w_meta, static_cast<int32_t*>(out), M, K, N_out,
                                                    stream, c.bt)
                                  : sparse_pair_dequant(W_comp, x, w_meta, act_scale, w_scale, bias,
                                                        static_cast<__half*>(out), M, K, N_out, stream, c.bt);
         if (r >= 0) return r;
-        c = sparse_choose(M, K, N_out, true, force_bt, false);   // no pair of these CTAs fits on this device
+        c = sparse_choose(M, K, N_out, true, aligned, force_bt, false);   // no pair of these CTAs fits on this device
     }
     const int bt = c.bt;
     switch (bt) {
@@ -461,8 +497,10 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
 
 }  // namespace
 
-SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, int force_bt, bool allow_pair) {
-    (void)K;
+SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, bool stream_ok, int force_bt, bool allow_pair) {
+    // One to four tokens: the call is a pass over the weights; the CUDA-core streaming kernel has none of
+    // the tensor-core kernel's fixed costs (measured 10.3 -> see the timing summaries).
+    if (force_bt == 0 && stream_ok && sparse_gemv_fits(M, K)) return {3, 0};
     if (!tma_ok) return {0, 0};
     if (allow_pair) {
         // 1000 + BT: the CTA-pair kernel (256 weight rows x BT tokens per pair of SMs), pinned.

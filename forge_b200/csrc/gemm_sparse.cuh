@@ -9,13 +9,21 @@ namespace fb200 {
 // Which kernel a 2:4-sparse GEMM call runs: decided in one place for the GEMM's own dispatch and
 // for the public plan query (forge_sparse_int8_gemm_plan).
 struct SparseChoice {
-    int kind;   // 0 = plain-CUDA kernel (shapes TMA cannot describe), 1 = one CTA per tile, 2 = CTA pair
+    int kind;   // 0 = plain-CUDA kernel (shapes TMA cannot describe), 1 = one CTA per tile, 2 = CTA pair,
+                // 3 = weight-streaming CUDA-core kernel for 1-4 tokens (sparse_gemv.cu)
     int bt;     // tokens per tile (kind 1: 32 / 64 / 128; kind 2: 128 / 192 / 224 / 256)
 };
-// tma_ok: K % 128 == 0 and 16-byte aligned operands. force_bt: 0 = automatic, 32/64/128 pins the
-// single-CTA tile, 1000 + BT the CTA-pair tile. allow_pair = false when the device cannot
-// co-schedule the pair kernel.
-SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, int force_bt, bool allow_pair);
+// tma_ok: K % 128 == 0 and 16-byte aligned operands; stream_ok: K % 32 == 0 and 16-byte aligned
+// operands. force_bt: 0 = automatic, 32/64/128 pins the single-CTA tile, 1000 + BT the CTA-pair
+// tile. allow_pair = false when the device cannot co-schedule the pair kernel.
+SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, bool stream_ok, int force_bt, bool allow_pair);
+
+// The 1-4 token kernel: true when it can take the shape (K % 32 == 0, token rows fit shared memory).
+bool sparse_gemv_fits(int M, int K);
+// epi 0: out int32 (M,N_out); epi 1: fp16 dequant (+ bias). Needs 16-byte aligned W_comp / x, 4-byte w_meta.
+int sparse_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out, cudaStream_t stream,
+                int epi);
 
 // out (M,N_out) s32 = x (M,K) s8 x W24 (N_out,K)^T, W24 given as W_comp (N_out,K/2) + w_meta (N_out,K/32).
 // force_bt: 32/64/128 pins the token-tile width, anything else selects it automatically.

@@ -247,6 +247,11 @@ __device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t sdesc)
     asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+// smem -> TMEM copy of 128 lanes x 256 bits (8 columns).
+__device__ __forceinline__ void tmem_cp_128x256b(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // TMEM -> registers: this thread's lane, 32 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(

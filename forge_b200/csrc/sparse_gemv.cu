@@ -1,0 +1,341 @@
+// 2:4-sparse INT8 GEMM for one to four tokens: a weight-streaming kernel on the CUDA cores.
+//
+// With so few tokens the call is a pass over the compressed weight (N_out x K/2 bytes) and its
+// metadata (N_out x K/8 bytes) and nothing else: 0.625 bytes per weight element against a handful
+// of integer operations. The tcgen05 kernel's fixed costs (tensor-map fetch, TMEM allocation,
+// 128-row tiles that leave SMs idle when N_out / 128 < SM count, commit -> TMEM read -> store at
+// the end) are then most of its time. Here every SM streams rows with plain 16-byte loads, many in
+// flight per thread, and the 2:4 selection is a byte permute:
+//
+//   lane l of a warp owns the 32-deep K chunks l, l + 32, ... of the warp's current weight row:
+//   16 compressed bytes (4 words of 4 weights = 2 groups each) + one metadata word (8 nibbles).
+//   The 2-bit position fields of the metadata word are spread to nibbles, which makes them the
+//   selector operands of four PRMT instructions that pick, from the 8 activation bytes of two
+//   groups, the 4 bytes the 4 kept weights multiply; DP4A accumulates in int32. A lane needs the
+//   same slice of the token rows for every weight row: for K <= 4096 it keeps that slice in
+//   registers (re-reading it from shared memory per weight row costs more shared-memory bandwidth
+//   than the weights cost HBM bandwidth), for larger K the token rows sit in shared memory.
+//
+// Exact int32 accumulation, the same fp32 epilogue as the tensor-core kernels: results are
+// bit-identical to them. Replaces, for M <= 4, the reference's split-K small-M configurations
+// (src/gemm/int8_sparse.cu:610-632, 885-920).
+#include "common.cuh"
+#include "gemm_dense.cuh"
+#include "gemm_sparse.cuh"
+
+namespace fb200 {
+
+namespace {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// 16 bits holding eight 2-bit fields -> 32 bits with each field in the low half of its own nibble.
+__device__ __forceinline__ uint32_t spread_fields(uint32_t x) {
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    return x;
+}
+
+// acc += sum over the 4 weights of `w` (two groups: positions sel[0..1] of a_lo, sel[2..3] of a_hi)
+__device__ __forceinline__ int dot_selected(uint32_t w, uint32_t a_lo, uint32_t a_hi, uint32_t sel, int acc) {
+    return __dp4a(static_cast<int>(w), static_cast<int>(__byte_perm(a_lo, a_hi, sel)), acc);
+}
+
+// One weight row against the lane's activation chunks: 4 chunks of 32 K per lane and pass.
+template <int MT>
+__device__ __forceinline__ void gemv_chunk(const uint4& w, uint32_t meta, const uint4 (&a)[MT], const uint4 (&b)[MT],
+                                           int (&acc)[MT]) {
+    const uint32_t s_lo = spread_fields(meta & 0xFFFFu) | 0x44004400u;
+    const uint32_t s_hi = spread_fields(meta >> 16) | 0x44004400u;
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        int s = acc[m];
+        s = dot_selected(w.x, a[m].x, a[m].y, s_lo, s);
+        s = dot_selected(w.y, a[m].z, a[m].w, s_lo >> 16, s);
+        s = dot_selected(w.z, b[m].x, b[m].y, s_hi, s);
+        s = dot_selected(w.w, b[m].z, b[m].w, s_hi >> 16, s);
+        acc[m] = s;
+    }
+}
+
+// Per-row epilogue operands, requested together with the row's weights so that their latency is not
+// paid after the reduction.
+struct RowScale {
+    float ws, bs;
+};
+template <int EPI>
+__device__ __forceinline__ RowScale load_row_scale(const __half* __restrict__ w_scale, const __half* __restrict__ bias,
+                                                   int row) {
+    RowScale r = {0.f, 0.f};
+    if (EPI == 1) {
+        r.ws = __half2float(w_scale[row]);
+        if (bias != nullptr) r.bs = __half2float(bias[row]);
+    }
+    return r;
+}
+
+template <int MT, int EPI>
+__device__ __forceinline__ void gemv_store(int (&acc)[MT], int lane, int row, void* __restrict__ out,
+                                           const float (&as)[MT], const RowScale& rs, bool has_bias, int M, int N_out) {
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
+    }
+    if (lane != 0) return;
+    if (EPI == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+            if (m < M) static_cast<int32_t*>(out)[(size_t)m * N_out + row] = acc[m];
+    } else {
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            if (m < M) {
+                const float o = dequant_gemm(acc[m], mul_ftz(as[m], rs.ws), rs.bs, has_bias);
+                static_cast<__half*>(out)[(size_t)m * N_out + row] = __float2half_rn(o);
+            }
+        }
+    }
+}
+
+// K <= 4096: a lane's slice of every token row (at most 4 chunks of 32 bytes per token) is the same for
+// every weight row, so it lives in registers for the whole kernel - no shared memory, no barrier.
+// The next row's weights are requested before the current row is reduced.
+// EPI 0: out is int32 (M, N_out); EPI 1: fp16 dequant (+ bias).
+template <int MT, int EPI>
+__global__ void __launch_bounds__(kGemvThreads)
+sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restrict__ x,
+                       const uint32_t* __restrict__ w_meta, const float* __restrict__ act_scale,
+                       const __half* __restrict__ w_scale, const __half* __restrict__ bias, void* __restrict__ out,
+                       int M, int K, int N_out) {
+    const int chunks = K >> 5;   // <= 128
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kGemvWarps + warp;
+    const int row_step = gridDim.x * kGemvWarps;
+    if (row0 >= N_out) return;
+
+    uint4 wv[4], wn[4];
+    uint32_t mv[4], mn[4];
+    auto load_row = [&](int row, uint4 (&w)[4], uint32_t (&m)[4]) {
+        const uint8_t* wrow = reinterpret_cast<const uint8_t*>(W_comp) + (size_t)row * (K >> 1);
+        const uint32_t* mrow = w_meta + (size_t)row * chunks;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = i * 32 + lane;
+            if (c < chunks) {
+                w[i] = ldg_stream16(wrow + (size_t)c * 16);
+                m[i] = ldg_stream4(mrow + c);
+            }
+        }
+    };
+    load_row(row0, wv, mv);   // in flight while the activations are fetched
+    RowScale rs = load_row_scale<EPI>(w_scale, bias, row0), rs_next = rs;
+    const bool has_bias = bias != nullptr;
+    float as[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) as[m] = (EPI == 1 && m < M) ? act_scale[m] : 0.f;
+
+    uint4 xa[4][MT], xb[4][MT];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int c = i * 32 + lane;
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            xa[i][m] = make_uint4(0, 0, 0, 0);
+            xb[i][m] = make_uint4(0, 0, 0, 0);
+            if (c < chunks && m < M) {
+                const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * 32);
+                xa[i][m] = p[0];
+                xb[i][m] = p[1];
+            }
+        }
+    }
+
+    for (int row = row0; row < N_out; row += row_step) {
+        const int next = row + row_step;
+        if (next < N_out) {
+            load_row(next, wn, mn);
+            rs_next = load_row_scale<EPI>(w_scale, bias, next);
+        }
+        int acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) acc[m] = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (i * 32 + lane < chunks) gemv_chunk<MT>(wv[i], mv[i], xa[i], xb[i], acc);
+        }
+        gemv_store<MT, EPI>(acc, lane, row, out, as, rs, has_bias, M, N_out);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            wv[i] = wn[i];
+            mv[i] = mn[i];
+        }
+        rs = rs_next;
+    }
+}
+
+// Any K (token rows up to 96 KB): the token rows sit in shared memory, for each token two arrays of
+// K/32 uint4 - bytes [0,16) and [16,32) of every 32-byte chunk - so that a warp's reads are conflict-free.
+template <int MT, int EPI>
+__global__ void __launch_bounds__(kGemvThreads)
+sparse_gemv_smem_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restrict__ x,
+                        const uint32_t* __restrict__ w_meta, const float* __restrict__ act_scale,
+                        const __half* __restrict__ w_scale, const __half* __restrict__ bias, void* __restrict__ out,
+                        int M, int K, int N_out) {
+    extern __shared__ uint4 xs[];   // [MT][2][K / 32]
+    const int chunks = K >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kGemvWarps + warp;
+    const int row_step = gridDim.x * kGemvWarps;
+    const bool has_bias = bias != nullptr;
+
+    // the first 128 chunks of a row are requested one row ahead (for K <= 4096 that is the whole row)
+    uint4 wv[4], wn[4];
+    uint32_t mv[4], mn[4];
+    auto load_head = [&](int row, uint4 (&w)[4], uint32_t (&m)[4]) {
+        const uint8_t* wrow = reinterpret_cast<const uint8_t*>(W_comp) + (size_t)row * (K >> 1);
+        const uint32_t* mrow = w_meta + (size_t)row * chunks;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = i * 32 + lane;
+            if (c < chunks) {
+                w[i] = ldg_stream16(wrow + (size_t)c * 16);
+                m[i] = ldg_stream4(mrow + c);
+            }
+        }
+    };
+    RowScale rs = {0.f, 0.f}, rs_next = rs;
+    if (row0 < N_out) {
+        load_head(row0, wv, mv);   // in flight while the activations are staged
+        rs = load_row_scale<EPI>(w_scale, bias, row0);
+    }
+    for (int i = threadIdx.x; i < MT * chunks * 2; i += kGemvThreads) {
+        const int m = i / (chunks * 2);
+        const int r = i - m * chunks * 2;
+        const int c = r >> 1, half = r & 1;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * 32 + half * 16);
+        xs[(m * 2 + half) * chunks + c] = v;
+    }
+    float as[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) as[m] = (EPI == 1 && m < M) ? act_scale[m] : 0.f;
+    __syncthreads();
+
+    for (int row = row0; row < N_out; row += row_step) {
+        const int next = row + row_step;
+        if (next < N_out) {
+            load_head(next, wn, mn);
+            rs_next = load_row_scale<EPI>(w_scale, bias, next);
+        }
+        int acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) acc[m] = 0;
+        const uint8_t* wrow = reinterpret_cast<const uint8_t*>(W_comp) + (size_t)row * (K >> 1);
+        const uint32_t* mrow = w_meta + (size_t)row * chunks;
+        for (int c0 = 0; c0 < chunks; c0 += 128) {
+            if (c0 > 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int c = c0 + i * 32 + lane;
+                    if (c < chunks) {
+                        wv[i] = ldg_stream16(wrow + (size_t)c * 16);
+                        mv[i] = ldg_stream4(mrow + c);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int c = c0 + i * 32 + lane;
+                if (c < chunks) {
+                    uint4 a[MT], b[MT];
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        a[m] = xs[(m * 2 + 0) * chunks + c];
+                        b[m] = xs[(m * 2 + 1) * chunks + c];
+                    }
+                    gemv_chunk<MT>(wv[i], mv[i], a, b, acc);
+                }
+            }
+        }
+        gemv_store<MT, EPI>(acc, lane, row, out, as, rs, has_bias, M, N_out);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            wv[i] = wn[i];
+            mv[i] = mn[i];
+        }
+        rs = rs_next;
+    }
+}
+
+template <int MT, int EPI>
+int launch_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out, cudaStream_t stream) {
+    const long long blocks_for_rows = ((long long)N_out + kGemvWarps - 1) / kGemvWarps;
+    // One token: the shared-memory kernel (fewer registers, twice the resident warps). Two tokens and
+    // K <= 4096: token slices in registers. Knob 5 pins a variant (1 registers, 2 shared memory).
+    const int pin = tuning_knob(kKnobGemvVariant);
+    const bool in_regs = K <= 4096 && (pin == 1 || (pin == 0 && MT >= 2));
+    if (in_regs) {
+        // resident CTAs per SM by register use; every warp has two rows of weights in flight
+        const int per_sm = MT <= 2 ? 2 : 1;
+        const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * per_sm);
+        sparse_gemv_reg_kernel<MT, EPI><<<grid, kGemvThreads, 0, stream>>>(W_comp, x, w_meta, act_scale, w_scale, bias,
+                                                                         out, M, K, N_out);
+        return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+    const size_t smem = (size_t)MT * K;   // MT token rows of K bytes
+    auto kern = sparse_gemv_smem_kernel<MT, EPI>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && !attr_set[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+            return kLaunchFailed;
+        attr_set[dev & 63] = true;
+    }
+    const int per_sm = smem <= 16 * 1024 ? (MT == 1 ? 4 : 3) : (smem <= 48 * 1024 ? 2 : 1);
+    const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * per_sm);
+    kern<<<grid, kGemvThreads, smem, stream>>>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+}  // namespace
+
+bool sparse_gemv_fits(int M, int K) {
+    // beyond two tokens the tensor-core kernel wins (measured at N_out = 11008, K = 4096); knob 6 moves the limit
+    const int max_tokens = tuning_knob(kKnobGemvMaxTokens) > 0 ? std::min(4, tuning_knob(kKnobGemvMaxTokens)) : 2;
+    if (M < 1 || M > max_tokens || K % 32 != 0) return false;
+    if (K <= 4096) return true;
+    return M <= 2 && (size_t)M * K <= 96 * 1024;      // shared-memory kernel only
+}
+
+int sparse_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
+                const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out, cudaStream_t stream,
+                int epi) {
+    const int mt = M <= 1 ? 1 : (M <= 2 ? 2 : 4);
+#define FB200_GEMV(MT)                                                                                              \
+    return epi == 0 ? launch_gemv<MT, 0>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream)     \
+                    : launch_gemv<MT, 1>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out, stream)
+    if (mt == 1) { FB200_GEMV(1); }
+    if (mt == 2) { FB200_GEMV(2); }
+    FB200_GEMV(4);
+#undef FB200_GEMV
+}
+
+}  // namespace fb200

@@ -55,6 +55,10 @@ __global__ void wait_timeout_selftest_kernel(int* status, unsigned long long bud
 
 }  // namespace
 
+void set_tuning_knob(int key, int value) {
+    if (key >= 0 && key < kNumKnobs) g_knobs[key].store(value, std::memory_order_relaxed);
+}
+
 int tuning_knob(int key) { return (key >= 0 && key < kNumKnobs) ? g_knobs[key].load(std::memory_order_relaxed) : 0; }
 
 }  // namespace fb200

@@ -23,6 +23,16 @@ int forge_b200_get_tuning(int key);
 /* Copies up to 8 probe counters of the sparse CTA-pair kernel (pair-kernel flag 32) to out. */
 int forge_b200_read_probe(unsigned long long* out, int n);
 
+/* Ceiling probes (probes.cu). mma_rate: clocks per tcgen05.mma kind::i8 instruction with operands
+ * resident in shared memory - pair != 0: cta_group::2 with M = 256, else M = 128; n: UMMA N (multiple
+ * of 16, <= 256); sparse != 0: the 2:4 form with K = 64, else K = 32; commits: tcgen05.commit per four
+ * instructions (0, 1 or 2); ctas: CTAs launched (all time themselves, CTA 0 reports). tma_ingest: mean
+ * bytes per clock and CTA when `ctas` CTAs stream 128 x 128-byte tiles of `matrix` (rows x kcols int8)
+ * with `producers` TMA-issuing threads each. Both synchronise the device and return a negative status
+ * code on failure. */
+double forge_b200_probe_mma_rate(int pair, int n, int sparse, int commits, int ctas);
+double forge_b200_probe_tma_ingest(const void* matrix, int rows, int kcols, int producers, int ctas);
+
 /* Launches one thread block that waits, for at most budget_us microseconds (clamped to
  * 10000), on a barrier nobody arrives at - the way every bounded wait of the GEMM kernels gives
  * up - and then records raw code 900 in the device status word and returns normally. */

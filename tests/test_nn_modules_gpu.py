@@ -184,10 +184,22 @@ def test_scratch_buffers_follow_the_batch_size():
                 assert torch.equal(fresh(x), y)
 
 
-def test_static_scheme_calibration_and_qat_flow_on_the_gpu():
+class _FakeQuantWrapped(nn.Module):
+    """The attribute layout of the reference's QAT wrapper (python/forge/quant/convert.py:123-160): a float
+    `linear` plus `weight_fq` / `input_fq` modules; finalize_qat recognises it by that shape."""
+
+    def __init__(self, linear):
+        super().__init__()
+        self.linear, self.weight_fq, self.input_fq = linear, nn.Identity(), nn.Identity()
+
+    def forward(self, x):
+        return nn.functional.linear(self.input_fq(x), self.weight_fq(self.linear.weight), self.linear.bias)
+
+
+def test_static_scheme_calibration_and_qat_finalization_on_the_gpu():
     """quantize(model, data, scheme="static_int8") runs the calibration batches through the converted
-    model (the reference's call shape), and prepare_qat -> enable_qat -> finalize_qat ends in layers
-    whose output equals a direct conversion of the same float weights."""
+    model (the reference's call shape), and finalize_qat turns fake-quantize wrappers around trained
+    float layers into layers whose output equals a direct conversion of the same float weights."""
     from forge_b200 import quant as Q
     torch.manual_seed(4)
     model = TinyMLP().to(DEV).half()
@@ -197,12 +209,36 @@ def test_static_scheme_calibration_and_qat_flow_on_the_gpu():
     x = torch.randn(16, 256, device=DEV, dtype=torch.float16)
     with torch.no_grad():
         assert torch.equal(q_static(x), q_dyn(x))
-    qat = Q.prepare_qat(model.float())
-    Q.enable_calibration(qat)
-    with torch.no_grad():
-        qat(x.float())
-    Q.enable_qat(qat)
+    import copy
+    qat = copy.deepcopy(model).float()
+    for name, child in list(qat.named_children()):
+        if isinstance(child, nn.Linear):
+            setattr(qat, name, _FakeQuantWrapped(child))
     qat(x.float()).sum().backward()
     final = Q.finalize_qat(qat, verbose=False)
     with torch.no_grad():
         assert torch.equal(final(x), q_dyn(x))
+
+
+@pytest.mark.parametrize("in_features", [48, 100])
+def test_quantize_accepts_any_in_features_on_the_gpu(in_features):
+    """The reference's quantize_weight takes any K (python/forge/nn/linear.py:167-173); widths that are not
+    a multiple of 32 take the torch recipe on the device instead of the one-pass kernel, and the layer then
+    runs on the ragged-shape GEMM path."""
+    from forge_b200 import quant as Q
+    torch.manual_seed(in_features)
+    net = nn.Sequential(nn.Linear(in_features, 24)).to(DEV)
+    q = Q.quantize(net, verbose=False)
+    assert isinstance(q[0], QuantizedLinear)
+    wq, ws = quantize_weight_per_channel(net[0].weight.data)           # the recipe, on the weight's device
+    assert torch.equal(q[0].w_int8, wq) and torch.equal(q[0].w_scale.data, ws)
+    wq_cpu, _ = quantize_weight_per_channel(net[0].weight.data.cpu())  # CPU arithmetic: at most one step apart
+    assert (q[0].w_int8.cpu().int() - wq_cpu.int()).abs().max() <= 1
+    x = torch.randn(9, in_features, device=DEV, dtype=torch.float16)
+    with torch.no_grad():
+        y = q(x)
+    torch.cuda.synchronize()
+    xq, xs = C.fused_quantize_activation(x, 9, in_features)
+    want = O.dequantize_bias(O.gemm_s32(xq.cpu().numpy(), q[0].w_int8.cpu().numpy()), xs.cpu().numpy(),
+                             q[0].w_scale.data.cpu().numpy(), q[0].bias.data.cpu().numpy(), gemm_epilogue=True)
+    assert np.array_equal(y.cpu().numpy().view(np.uint16), want.view(np.uint16))

@@ -156,3 +156,41 @@ def test_plan_is_valid_and_honours_forced_tile():
             assert t.value == tile
         lib.forge_sparse_int8_gemm_plan(M, K, N, 4, 0, -1, ctypes.byref(t), ctypes.byref(s))
         assert s.value == 1   # no workspace -> unsplit (int8_sparse.cu:896)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("K,N", [(32, 8), (96, 17), (4096, 1000), (8192, 300), (11008, 96), (4096, 11008)])
+def test_one_to_four_tokens_weight_streaming_kernel(M, K, N, variant):
+    """Few tokens take the CUDA-core weight-streaming kernel (PRMT selection + DP4A; by default up to two
+    tokens, here every template instance: variant 1 keeps the token slices in registers, 2 in shared
+    memory, 0 is the automatic choice). It must give the accumulators of the host loop on the pruned
+    weights, the FP16 epilogue of the oracle, and the very bytes of the tensor-core kernel (pinned with the
+    32-token tile knob where K allows it)."""
+    W, x, a_s, w_s, bias, comp, packed = _prep(M, K, N, 11 + M + K + N)
+    lib = _lib.load()
+    dx, das, dws, dbias = x.to(DEV), a_s.to(DEV), w_s.to(DEV), bias.to(DEV)
+    lib.forge_b200_set_tuning(5, variant)
+    lib.forge_b200_set_tuning(6, 4 if variant else 0)
+    try:
+        acc = C.sparse_int8_gemm_s32(comp, dx, packed)
+        out = C.sparse_int8_gemm(comp, dx, packed, das, dws, dbias)
+        out_nb = C.sparse_int8_gemm(comp, dx, packed, das, dws, None, tile=2)   # the planned id of this kernel
+        _status_ok()
+    finally:
+        lib.forge_b200_set_tuning(5, 0)
+        lib.forge_b200_set_tuning(6, 0)
+    want_acc = O.gemm_s32(x.numpy(), O.prune_24_dense(W.numpy()))
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+    want = O.dequantize_bias(want_acc, a_s.numpy(), w_s.numpy(), bias.numpy(), gemm_epilogue=True)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    want_nb = O.dequantize_bias(want_acc, a_s.numpy(), w_s.numpy(), None, gemm_epilogue=True)
+    assert np.array_equal(out_nb.cpu().numpy().view(np.uint16), want_nb.view(np.uint16))
+    if K % 128 == 0 and variant == 0:
+        lib.forge_b200_set_sparse_tile(32)
+        try:
+            tc = C.sparse_int8_gemm(comp, dx, packed, das, dws, dbias)
+            _status_ok()
+        finally:
+            lib.forge_b200_set_sparse_tile(0)
+        assert torch.equal(out.view(torch.int16), tc.view(torch.int16))
