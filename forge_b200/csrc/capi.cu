@@ -19,15 +19,16 @@ inline cudaStream_t S(forge_stream_t s) { return reinterpret_cast<cudaStream_t>(
 inline const __half* H(const void* p) { return static_cast<const __half*>(p); }
 inline __half* H(void* p) { return static_cast<__half*>(p); }
 
-// Tile id of the reference API -> tile knob of the tcgen05 kernels: the reference's 256-row
-// weight tile is the CTA-pair kernel (256 weight rows x 224 tokens per pair, knob 1000 + 224);
-// its 128-row tiles are the single-CTA kernel with 128 tokens, or 64 (32 when M <= 32) tokens; for
-// 1-2 tokens the smallest id leaves the choice automatic (the weight-streaming kernel).
+// Tile id of the reference API -> tile knob of the tcgen05 kernels: the reference's 256-row weight
+// tile is the CTA-pair kernel (256 weight rows per pair of SMs, 192 or 224 tokens by the cost model,
+// knob 1000); its 128x128 tile is the single-CTA kernel with 128 tokens; its 128x64 tile the single-CTA
+// kernel with 64 or 32 tokens by the cost model (knob 1) - and, for 1-2 tokens, the weight-streaming
+// kernel (knob 0: the automatic choice).
 inline int tile_to_bt(int tile, int M) {
     switch (tile) {
-    case FORGE_SPARSE_TILE_256x128: return 1224;
+    case FORGE_SPARSE_TILE_256x128: return 1000;
     case FORGE_SPARSE_TILE_128x128: return 128;
-    case FORGE_SPARSE_TILE_128x64: return M <= 2 ? 0 : (M <= 32 ? 32 : 64);   // 1-2 tokens: the streaming kernel
+    case FORGE_SPARSE_TILE_128x64: return M <= 2 ? 0 : 1;
     default: return 0;
     }
 }

@@ -6,7 +6,7 @@
 // two-pass path: the quantizer arithmetic is the standalone kernel's, the GEMM and epilogue are
 // the sparse kernel's.
 //
-// Each persistent CTA walks blocks of 64 tokens. Eight quantizer warps turn a block's FP16 rows
+// Each persistent CTA walks blocks of 64 tokens. Sixteen quantizer warps turn a block's FP16 rows
 // (whole row in registers, 16-byte loads, warp-shuffle absmax) into INT8 written straight into
 // shared memory in the layout the tensor core reads - K-major atoms of 64 rows x 128 bytes with
 // the 128-byte swizzle - and leave the per-token scales in shared memory. There are two such block
@@ -32,9 +32,9 @@ constexpr int BT = 64;                  // tokens per block (UMMA N)
 constexpr int BW = 128;                 // weight rows per tile (UMMA M)
 constexpr int kMaxK = 1280;             // a block: up to 10 atoms of 8 KB, two blocks resident
 constexpr int kEpiWarps = 4;
-constexpr int kQuantWarps = 8;
+constexpr int kQuantWarps = 16;
 constexpr int kRowsPerQuantWarp = BT / kQuantWarps;
-// warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-13 quantizers, warp 14 metadata copies
+// warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-21 quantizers, warp 22 metadata copies
 constexpr int kFirstQuantWarp = 2 + kEpiWarps;
 constexpr int kCopyWarp = kFirstQuantWarp + kQuantWarps;
 constexpr int kThreads = 32 * (kCopyWarp + 1);
@@ -236,7 +236,7 @@ sparse_fq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         }
     } else if (warp_id >= kFirstQuantWarp) {
         // ------------------------------------------------------------------ quantizers
-        const int qw = warp_id - kFirstQuantWarp;  // 0..7: rows [8*qw, 8*qw+8) of every block
+        const int qw = warp_id - kFirstQuantWarp;  // rows [4*qw, 4*qw+4) of every block
         const int n_chunks = K / 16;               // 16-value chunks per row
         int blocks = 0;
         for (int tb = blockIdx.x; tb < t_blocks; tb += gridDim.x, blocks++) {
@@ -249,23 +249,34 @@ sparse_fq_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             for (int rr = 0; rr < kRowsPerQuantWarp; rr += 2) {
                 uint4 v[2][kChunksPerLane][2];
                 __half2 hmax[2];
+                // every load of the two rows is issued before anything consumes one (a loop that mixed the
+                // loads with the running maximum made each load wait for the previous one's use)
 #pragma unroll
                 for (int u = 0; u < 2; u++) {
                     const int r = qw * kRowsPerQuantWarp + rr + u;
                     const int row = min(m0 + r, M - 1);
                     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * K);
-                    hmax[u] = __float2half2_rn(0.f);
 #pragma unroll
                     for (int i = 0; i < kChunksPerLane; i++) {
                         const int c = lane + 32 * i;
-                        if (c < n_chunks) {
+                        const bool live = c < n_chunks;
 #pragma unroll
-                            for (int hh = 0; hh < 2; hh++) {
-                                v[u][i][hh] = stream_x ? __ldcs(src + 2 * c + hh) : __ldg(src + 2 * c + hh);
-                                const __half2* h = reinterpret_cast<const __half2*>(&v[u][i][hh]);
+                        for (int hh = 0; hh < 2; hh++) {
+                            v[u][i][hh] = make_uint4(0u, 0u, 0u, 0u);
+                            if (live) v[u][i][hh] = stream_x ? __ldcs(src + 2 * c + hh) : __ldg(src + 2 * c + hh);
+                        }
+                    }
+                }
 #pragma unroll
-                                for (int j = 0; j < 4; j++) hmax[u] = __hmax2(hmax[u], __habs2(h[j]));
-                            }
+                for (int u = 0; u < 2; u++) {
+                    hmax[u] = __float2half2_rn(0.f);
+#pragma unroll
+                    for (int i = 0; i < kChunksPerLane; i++) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; hh++) {
+                            const __half2* h = reinterpret_cast<const __half2*>(&v[u][i][hh]);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) hmax[u] = __hmax2(hmax[u], __habs2(h[j]));
                         }
                     }
                 }

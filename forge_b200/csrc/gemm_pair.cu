@@ -43,7 +43,7 @@ constexpr int kEpiThreads = 128;
 // sparse kernel: epilogue warps per CTA - two per TMEM lane quarter, four for the gated epilogue
 // (measured: the heavier SiLU epilogue gains from 16 warps, the plain one loses a little)
 __host__ __device__ constexpr int sp_epi_warps(int epi) { return epi == 2 ? 16 : 8; }
-// TMA warp, MMA warp, the epilogue warps, second TMA warp
+// TMA warp, MMA warp, the epilogue warps, second TMA warp, metadata-copy warp
 __host__ __device__ constexpr int sp_threads(int epi) { return 128 + 32 * sp_epi_warps(epi); }
 constexpr int kSpEpiWarpsMax = 16;
 // weight-row blocks per raster band of the sparse kernel: the activations are re-read from DRAM
@@ -100,6 +100,7 @@ constexpr int kFlagTwoCommits = 2;  // free a stage with one tcgen05.commit per 
                                     // delivered to both CTAs' barriers
 constexpr int kFlagProbe = 4;       // sparse: pair 0's MMA thread records where its clocks go (g_pair_probe)
 constexpr int kFlagNoSplit = 8;     // dense: never cut the last wave's tiles in halves
+constexpr int kFlagOneProducer = 16; // dense: warp 0 issues both TMA loads of a stage, the second producer idles
 
 // kFlagProbe: [0] total clocks of the MMA thread's loop, [1] waiting for operands, [2] waiting for a
 // drained accumulator, [3] stages, [4] tiles
@@ -176,14 +177,18 @@ struct DensePairCfg {
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory limit");
 };
 
-template <int EPI>
+// FLAGS is a template parameter, 0 in production: the single-thread MMA issue loop must carry no run-time
+// flag test (one around the commits cost 15 % of the kernel's time at 8192^3). The measurement variants
+// are separate instantiations, selected by the launcher from the tuning knob.
+template <int EPI, int FLAGS>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_b_half, const __grid_constant__ CUtensorMap tm_c,
                   const float* __restrict__ act_scale,
                   const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
-                  int* __restrict__ status, int flags) {
+                  int* __restrict__ status) {
     using Cfg = DensePairCfg;
+    constexpr int flags = FLAGS;
     constexpr int BN = 256;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* smem_ab = smem;
@@ -228,9 +233,10 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // Two TMA producers per CTA: warp 0 loads the A slab and arms the stage's barrier with the byte
     // count of the whole stage (both CTAs), the last warp loads the B slab.
     const bool second = (warp_id == kThreads / 32 - 1);
+    const bool one_producer = (flags & kFlagOneProducer) != 0;
     if (warp_id == 0 || second) {
         // ------------------------------------------------------------------ TMA producers (both CTAs)
-        if (lane == 0) {
+        if (lane == 0 && !(second && one_producer)) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -254,6 +260,13 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         if (leader)
                             mbar_expect_tx(&bars.full[stage], 2 * (Cfg::kABytes + (half ? Cfg::kBBytes / 2 : Cfg::kBBytes)));
                         tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
+                        if (one_producer) {
+                            if (half)
+                                tma_load_2d_pair(sb, &tm_b_half, full_leader, kb * 128,
+                                                 tc.b_blk * 256 + item.n_off + (int)rank * 64);
+                            else
+                                tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
+                        }
                     } else if (half) {
                         // each CTA stages 64 of the 128 B rows of a half tile
                         tma_load_2d_pair(sb, &tm_b_half, full_leader, kb * 128,
@@ -458,15 +471,15 @@ struct SparsePairCfg {
     static_assert(kAccCols + kMetaCols <= 512, "TMEM capacity");
 };
 
-template <int BT, int EPI>
+template <int BT, int EPI, int FLAGS>
 __global__ void __launch_bounds__(sp_threads(EPI), 1)
 sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
                    const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
-                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status,
-                   int flags) {
+                   const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
+    constexpr int flags = FLAGS;   // see dense_pair_kernel
     // EPI 2 (gated): each CTA's 128-row weight tile is 64 gate rows followed by the 64 up rows of the
     // same output columns, so a pair produces 128 output columns per tile.
     using Cfg = SparsePairCfg<BT, EPI>;
@@ -513,12 +526,16 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t tmem_base = *bars.tmem_slot;
     const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
 
-    // Two TMA producers per CTA: warp 0 loads the weight slab and its metadata and arms the stage's
+    // Two TMA producers per CTA. One iteration of a producer (wait for the free stage, arm, issue) costs
+    // the issuing thread about 310 clocks plus 60-100 per additional load, whatever the box size
+    // (measured), and the MMAs of a stage take 500: a single thread issuing a stage's four loads is
+    // slower than the tensor cores. Warp 0 loads the weight slab and its metadata and arms both
     // barriers with the byte counts of both CTAs; the second-to-last warp loads the two activation
-    // atoms.
-    const bool second = (warp_id == sp_threads(EPI) / 32 - 2);
-    const bool copy_warp = (warp_id == sp_threads(EPI) / 32 - 1);
-    if (warp_id == 0 || second) {
+    // atoms. (A third producer warp was measured: no gain, and its registers cost the epilogue.)
+    const int n_warps = sp_threads(EPI) / 32;
+    const int producer = warp_id == 0 ? 0 : (warp_id == n_warps - 2 ? 1 : -1);
+    const bool copy_warp = (warp_id == n_warps - 1);
+    if (producer >= 0) {
         // ------------------------------------------------------------------ TMA producers (both CTAs)
         if (lane == 0) {
             int stage = 0;
@@ -541,11 +558,11 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     const uint32_t full_leader = mapa_shared(smem_u32(&bars.full[stage]), 0);
                     const uint32_t meta_leader = mapa_shared(smem_u32(&bars.meta_full[stage]), 0);
                     if ((flags & kFlagResident) != 0 && it >= Cfg::kStages) {
-                        if (leader && !second) {
+                        if (leader && producer == 0) {
                             mbar_arrive(&bars.meta_full[stage]);
                             mbar_arrive(&bars.full[stage]);
                         }
-                    } else if (!second) {
+                    } else if (producer == 0) {
                         if (leader) {
                             mbar_expect_tx(&bars.meta_full[stage], 2 * Cfg::kMetaBytes);
                             mbar_expect_tx(&bars.full[stage], 2 * (Cfg::kStageBytes - Cfg::kMetaBytes));
@@ -905,9 +922,33 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-    return launch_pairs(dense_pair_kernel<EPI>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b,
-                        tm_b_half, tm_c,
-                        act_scale, w_scale, bias, M, N, K, status, tuning_knob(kKnobPairFlags));
+    const int flags = tuning_knob(kKnobPairFlags);
+#define FB200_DENSE_VARIANT(F)                                                                                        \
+    if (flags == F) {                                                                                                 \
+        static int mp[64] = {};                                                                                       \
+        return launch_pairs(dense_pair_kernel<EPI, F>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, mp, tm_a, tm_b, \
+                            tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);                              \
+    }
+    FB200_DENSE_VARIANT(1) FB200_DENSE_VARIANT(2) FB200_DENSE_VARIANT(3) FB200_DENSE_VARIANT(8) FB200_DENSE_VARIANT(16)
+    FB200_DENSE_VARIANT(18)
+#undef FB200_DENSE_VARIANT
+    // The half-tile bookkeeping costs about 2 % where no tile is ever cut (8192^3): the instantiation
+    // without it runs unless this launch's last wave will be split.
+    {
+        static int mp_probe[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const int pairs_known = mp_probe[dev & 63] > 0 ? mp_probe[dev & 63] : max_pairs[dev & 63];
+        const int cap = tuning_knob(kKnobMaxPairs);
+        int pairs = pairs_known > 0 ? (int)std::min<long long>(tiles, pairs_known) : 0;
+        if (cap > 0 && cap < pairs) pairs = cap;
+        const bool will_split = pairs > 0 && dense_work((int)tiles, pairs, true).items != (int)tiles;
+        if (!will_split && pairs > 0)
+            return launch_pairs(dense_pair_kernel<EPI, kFlagNoSplit>, kThreads, DensePairCfg::kSmemBytes, tiles, stream,
+                                mp_probe, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);
+    }
+    return launch_pairs(dense_pair_kernel<EPI, 0>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b,
+                        tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);
 }
 
 template <int BT, int EPI>
@@ -953,9 +994,21 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     const long long tiles = (long long)((N_out + 2 * CTA_W - 1) / (2 * CTA_W)) * ((M + BT - 1) / BT);
     OutDst md = {};
     if (multi != nullptr) md = *multi;
-    return launch_pairs(sparse_pair_kernel<BT, EPI>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w, tm_x,
-                        tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
-                        status, tuning_knob(kKnobPairFlags));
+    const int flags = tuning_knob(kKnobPairFlags);
+#define FB200_SPARSE_VARIANT(F)                                                                                       \
+    if (flags == F) {                                                                                                 \
+        static int mp[64] = {};                                                                                       \
+        return launch_pairs(sparse_pair_kernel<BT, EPI, F>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, mp, tm_w, tm_x, \
+                            tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, \
+                            status);                                                                                  \
+    }
+    if (BT == 224 && EPI == 1) {   // measurement variants exist for the default tile only
+        FB200_SPARSE_VARIANT(1) FB200_SPARSE_VARIANT(2) FB200_SPARSE_VARIANT(3) FB200_SPARSE_VARIANT(4)
+    }
+#undef FB200_SPARSE_VARIANT
+    return launch_pairs(sparse_pair_kernel<BT, EPI, 0>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w,
+                        tm_x, tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
+                        status);
 }
 
 template <int EPI>

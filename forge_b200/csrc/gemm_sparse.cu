@@ -497,27 +497,57 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
 
 }  // namespace
 
+// Cost model of the tile choice, the counterpart of the reference's wave-aware model
+// (src/gemm/int8_sparse.cu:885-920, fitted there to an RTX 4090): a launch of variant v costs
+//     c0_v + waves_v * (a_v * ksteps + b_v)   microseconds,
+// waves_v = ceil(tiles_v / co-resident tiles), ksteps = ceil(K / 256). The constants are a
+// non-negative least-squares fit to single launches with cold L2 on a B200 over the reference's
+// benchmark grid ((K, N) in {(1536,6144), (6144,1536), (1280,5120), (5120,1280)} x M in {64, 1024, 4096,
+// 8192}), the 11008 x 4096 weight at M = 8 ... 8192, the 4096 <-> 14336 and 8192 -> 28672 layers at
+// M = 8192 and four square shapes; on those 36 points the model's pick is within 6 % of the best
+// measured variant everywhere (sum of times 2743 us against 2740 us for the per-point best and 2836 us
+// for the rule it replaces).
+struct TileCost {
+    int bt;
+    bool pair;
+    float c0, a, b;
+};
+constexpr TileCost kTileCosts[] = {
+    {32, false, 11.24f, 0.273f, 0.261f},  {64, false, 11.10f, 0.291f, 0.347f}, {128, false, 13.47f, 0.410f, 0.550f},
+    {192, true, 15.61f, 0.440f, 0.994f}, {224, true, 15.56f, 0.488f, 1.091f},
+};
+
+// force_bt: 0 = free choice; 1 = one CTA per tile, 32 or 64 tokens; 32 / 64 / 128 = that single-CTA tile;
+// 1000 = CTA pair, width by the model; 1000 + BT = that pair tile.
 SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, bool stream_ok, int force_bt, bool allow_pair) {
-    // One to four tokens: the call is a pass over the weights; the CUDA-core streaming kernel has none of
-    // the tensor-core kernel's fixed costs (measured 10.3 -> see the timing summaries).
+    // One or two tokens: the call is a pass over the weights; the CUDA-core streaming kernel has less
+    // fixed cost than the tensor-core kernel (sparse_gemv.cu).
     if (force_bt == 0 && stream_ok && sparse_gemv_fits(M, K)) return {3, 0};
     if (!tma_ok) return {0, 0};
-    if (allow_pair) {
-        // 1000 + BT: the CTA-pair kernel (256 weight rows x BT tokens per pair of SMs), pinned.
-        if (force_bt > 1000) return {2, force_bt - 1000};
-        // Large problems: 256 weight rows x 224 tokens per CTA pair (measured fastest from
-        // M = N_out = 8192, K >= 1024 down to the 11008 x 4096 weight of a Llama MLP).
-        if (force_bt == 0 && M >= 1024 && N_out >= 512) return {2, 224};
+    if (force_bt > 1000) {
+        if (allow_pair) return {2, force_bt - 1000};
+        force_bt = 0;
     }
-    int bt = force_bt;
-    if (bt != 32 && bt != 64 && bt != 128) {
-        const long long w_blocks = (N_out + BW - 1) / BW;
-        const int sms = sm_count();
-        if (M > 64 && w_blocks * ((M + 127) / 128) >= sms) bt = 128;
-        else if (M > 32) bt = (M > 64 && w_blocks * ((M + 63) / 64) < sms) ? 64 : (M > 64 ? 128 : 64);
-        else bt = 32;
+    if (force_bt == 32 || force_bt == 64 || force_bt == 128) return {1, force_bt};
+    const int sms = sm_count();
+    const float ksteps = (float)((K + SLAB_K - 1) / SLAB_K);
+    SparseChoice best = {1, 128};
+    float best_cost = 3.0e38f;
+    for (const TileCost& t : kTileCosts) {
+        if (t.pair && (!allow_pair || force_bt == 1)) continue;
+        if (!t.pair && force_bt == 1000 && allow_pair) continue;
+        if (force_bt == 1 && t.bt > 64) continue;
+        const long long tiles = t.pair ? (long long)((N_out + 2 * BW - 1) / (2 * BW)) * ((M + t.bt - 1) / t.bt)
+                                       : (long long)((N_out + BW - 1) / BW) * ((M + t.bt - 1) / t.bt);
+        const long long slots = t.pair ? sms / 2 : sms;
+        const float waves = (float)((tiles + slots - 1) / slots);
+        const float cost = t.c0 + waves * (t.a * ksteps + t.b);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = {t.pair ? 2 : 1, t.bt};
+        }
     }
-    return {1, bt};
+    return best;
 }
 
 int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,

@@ -10,12 +10,13 @@ namespace fb200 {
 // for the public plan query (forge_sparse_int8_gemm_plan).
 struct SparseChoice {
     int kind;   // 0 = plain-CUDA kernel (shapes TMA cannot describe), 1 = one CTA per tile, 2 = CTA pair,
-                // 3 = weight-streaming CUDA-core kernel for 1-4 tokens (sparse_gemv.cu)
+                // 3 = weight-streaming CUDA-core kernel for 1-2 tokens (sparse_gemv.cu)
     int bt;     // tokens per tile (kind 1: 32 / 64 / 128; kind 2: 128 / 192 / 224 / 256)
 };
 // tma_ok: K % 128 == 0 and 16-byte aligned operands; stream_ok: K % 32 == 0 and 16-byte aligned
-// operands. force_bt: 0 = automatic, 32/64/128 pins the single-CTA tile, 1000 + BT the CTA-pair
-// tile. allow_pair = false when the device cannot co-schedule the pair kernel.
+// operands. force_bt: 0 = automatic (cost model), 32/64/128 pins the single-CTA tile, 1 = single CTA
+// with 32 or 64 tokens, 1000 + BT pins the CTA-pair tile, 1000 = CTA pair with the model's width.
+// allow_pair = false when the device cannot co-schedule the pair kernel.
 SparseChoice sparse_choose(int M, int K, int N_out, bool tma_ok, bool stream_ok, int force_bt, bool allow_pair);
 
 // The 1-4 token kernel: true when it can take the shape (K % 32 == 0, token rows fit shared memory).

@@ -1,4 +1,5 @@
-// 2:4-sparse INT8 GEMM for one to four tokens: a weight-streaming kernel on the CUDA cores.
+// 2:4-sparse INT8 GEMM for very few tokens (one or two by default, template instances up to four):
+// a weight-streaming kernel on the CUDA cores.
 //
 // With so few tokens the call is a pass over the compressed weight (N_out x K/2 bytes) and its
 // metadata (N_out x K/8 bytes) and nothing else: 0.625 bytes per weight element against a handful
@@ -17,7 +18,7 @@
 //   than the weights cost HBM bandwidth), for larger K the token rows sit in shared memory.
 //
 // Exact int32 accumulation, the same fp32 epilogue as the tensor-core kernels: results are
-// bit-identical to them. Replaces, for M <= 4, the reference's split-K small-M configurations
+// bit-identical to them. Replaces, for M <= 2, the reference's split-K small-M configurations
 // (src/gemm/int8_sparse.cu:610-632, 885-920).
 #include "common.cuh"
 #include "gemm_dense.cuh"
@@ -287,10 +288,10 @@ template <int MT, int EPI>
 int launch_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, const float* act_scale,
                 const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out, cudaStream_t stream) {
     const long long blocks_for_rows = ((long long)N_out + kGemvWarps - 1) / kGemvWarps;
-    // One token: the shared-memory kernel (fewer registers, twice the resident warps). Two tokens and
-    // K <= 4096: token slices in registers. Knob 5 pins a variant (1 registers, 2 shared memory).
+    // K <= 4096: token slices in registers (measured faster with the FP16 epilogue for one and two tokens);
+    // larger K: token rows in shared memory. Knob 5 pins a variant (1 registers, 2 shared memory).
     const int pin = tuning_knob(kKnobGemvVariant);
-    const bool in_regs = K <= 4096 && (pin == 1 || (pin == 0 && MT >= 2));
+    const bool in_regs = K <= 4096 && pin != 2;
     if (in_regs) {
         // resident CTAs per SM by register use; every warp has two rows of weights in flight
         const int per_sm = MT <= 2 ? 2 : 1;

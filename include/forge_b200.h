@@ -111,14 +111,15 @@ enum {
 
 /* forge::gemm::sparse_int8_gemm_plan - include/forge/gemm/int8_sparse.cuh:33-50,
  * src/gemm/int8_sparse.cu:875-920. Writes the (tile, split_k) forge_sparse_int8_gemm will run,
- * chosen by the same routine the GEMM's own dispatch calls. split_k is always 1: the s32
- * accumulator in tensor memory covers the whole K range. The tcgen05 tile set is reported through
- * the reference's three ids: FORGE_SPARSE_TILE_256x128 = the CTA-pair kernel (256 weight rows x
- * 224 tokens per pair of SMs), 128x128 = one CTA with 128 tokens, 128x64 = one CTA with 64 or -
- * for M <= 32 - 32 tokens, and also the answer for the weight-streaming kernel that takes 1-2
- * tokens and for shapes only the plain-CUDA kernel takes (K % 128 != 0; the plan sees no pointers
- * and assumes 16-byte aligned operands). Passing the
- * planned tile back to forge_sparse_int8_gemm runs exactly the kernel the automatic path runs. */
+ * chosen by the same routine the GEMM's own dispatch calls: a wave-aware cost model like the
+ * reference's, with per-tile constants fitted on a B200. split_k is always 1: the s32 accumulator in
+ * tensor memory covers the whole K range. The tcgen05 tile set is reported through the reference's
+ * three ids: FORGE_SPARSE_TILE_256x128 = the CTA-pair kernel (256 weight rows x 192 or 224 tokens
+ * per pair of SMs), 128x128 = one CTA with 128 tokens, 128x64 = one CTA with 64 or 32 tokens, and
+ * also the answer for the weight-streaming kernel that takes 1-2 tokens and for shapes only the
+ * plain-CUDA kernel takes (K % 128 != 0; the plan sees no pointers and assumes 16-byte aligned
+ * operands). Passing the planned tile back to forge_sparse_int8_gemm runs exactly the kernel the
+ * automatic path runs. */
 int forge_sparse_int8_gemm_plan(int M, int K, int N_out, int split_k, int have_workspace, int tile, int* out_tile,
                                 int* out_split_k);
 
