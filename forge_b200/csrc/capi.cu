@@ -133,17 +133,19 @@ int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uin
                                S(stream), bt);
 }
 
-// Policy of the automatic path (the reference's is sp_use_fused, src/gemm/int8_sparse.cu:930-938,
-// which fuses narrow layers whose activation does not fit L2 on an RTX 4090). On B200 the two-pass
-// path won every measured shape - at the reference's showcase shape (M = 147456, K = 1280,
-// N_out = 320) 0.18 ms against 0.36 ms for the fused kernel, whose quantize prologue cannot overlap
-// the MMAs on its single resident block - so the automatic path never fuses. The fused kernel
-// stays available through kSparseLinearFused (bit-identical output, no scratch buffers).
+// Policy of the automatic path (the reference's is sp_use_fused, src/gemm/int8_sparse.cu:930-938: it fuses
+// narrow layers whose activation does not fit L2 on an RTX 4090). Measured on B200 at M = 147456 the
+// fused kernel beats quantize + pair GEMM for every K <= 1280 when N_out <= 640 (7-26 %: K = 1280,
+// N_out = 320, the reference's showcase shape, 0.162 against 0.175 ms) and for K <= 1024 up to N_out = 1280
+// (6-9 %); it loses at K = 1280, N_out = 1280 (its 64-token blocks re-stream the weights twice as often as
+// the pair kernel's tiles and its N = 64 instructions run at a third of the tensor rate) and is on par or
+// slower while the FP16 activation still fits L2 (M = 32768, K = 1280: 53 against 52 us; M = 2048: 22
+// against 17 us). Hence: fuse when the kernel can take K, the activation does not fit L2, and the
+// layer is narrow.
 int forge_sparse_int8_linear_fused(int M, int K, int N_out) {
-    (void)M;
-    (void)K;
-    (void)N_out;
-    return 0;
+    if (M <= 0 || N_out <= 0 || K <= 0 || K % 128 != 0 || K > 1280) return 0;
+    if ((size_t)M * K * 2 <= l2_bytes()) return 0;
+    return (N_out <= 640 || (N_out <= 1280 && K <= 1024)) ? 1 : 0;
 }
 
 int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t* w_meta, const void* w_scale,

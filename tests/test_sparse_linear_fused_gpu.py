@@ -86,8 +86,31 @@ def test_fused_needs_k_up_to_1280_else_two_pass_with_scratch():
 
 
 def test_auto_policy():
-    """On B200 the two-pass path is the faster one at every measured shape, so the automatic path
-    reports 'not fused' everywhere (the reference's RTX 4090 model fuses its showcase shape)."""
+    """The automatic path fuses narrow layers (N_out <= 640, or <= 1280 with K <= 1024) with K <= 1280 whose
+    FP16 activation does not fit L2 - where the fused kernel measured faster than quantize + GEMM on B200 -
+    and nothing else (the reference's rule has the same form, src/gemm/int8_sparse.cu:930-938)."""
     lib = _lib.load()
-    for shape in [(147456, 1280, 320), (4096, 1280, 5120), (5000, 1024, 336), (100000, 4096, 320)]:
-        assert lib.forge_sparse_int8_linear_fused(*shape) == 0
+    expect = {(147456, 1280, 320): 1, (147456, 512, 128): 1, (147456, 1024, 1280): 1, (147456, 1280, 1280): 0,
+              (4096, 1280, 5120): 0, (5000, 1024, 336): 0, (100000, 4096, 320): 0, (32768, 1280, 320): 0}
+    for shape, want in expect.items():
+        assert lib.forge_sparse_int8_linear_fused(*shape) == want, shape
+
+
+def test_auto_path_takes_the_fused_kernel_where_the_policy_says_so():
+    """At a shape the policy fuses, the automatic path must not touch the scratch buffers (the fused kernel
+    has none) and must give the two-pass bytes."""
+    M, K, N = 60000, 1280, 320          # 154 MB of FP16 activations: beyond L2
+    lib = _lib.load()
+    assert lib.forge_sparse_int8_linear_fused(M, K, N) == 1
+    W, x, w_s, bias, comp, meta = _prep(M, K, N, 77)
+    dx, dws, dbias = x.to(DEV), w_s.to(DEV), bias.to(DEV)
+    two, _, _ = _linear(dx, comp, meta, dws, dbias, TWO_PASS)
+    out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    sq = torch.full((M, K), 0x5A, dtype=torch.int8, device=DEV)
+    ss = torch.full((M,), -7.0, dtype=torch.float32, device=DEV)
+    _lib.call("forge_sparse_int8_linear", dx.data_ptr(), comp.data_ptr(), meta.data_ptr(), dws.data_ptr(),
+              dbias.data_ptr(), out.data_ptr(), M, K, N, sq.data_ptr(), ss.data_ptr(), 0, 1, 0, AUTO)
+    torch.cuda.synchronize()
+    assert C.device_status() == 0
+    assert torch.equal(out.view(torch.int16), two.view(torch.int16))
+    assert int(sq.min()) == 0x5A and int(sq.max()) == 0x5A and float(ss.min()) == -7.0   # scratch untouched
