@@ -101,6 +101,12 @@ constexpr int kFlagTwoCommits = 2;  // free a stage with one tcgen05.commit per 
 constexpr int kFlagProbe = 4;       // sparse: pair 0's MMA thread records where its clocks go (g_pair_probe)
 constexpr int kFlagNoSplit = 8;     // dense: never cut the last wave's tiles in halves
 constexpr int kFlagOneProducer = 16; // dense: warp 0 issues both TMA loads of a stage, the second producer idles
+constexpr int kFlagNoEpilogue = 32;  // sparse: the epilogue warps free the accumulator without reading or storing it
+constexpr int kFlagNoMetaCopy = 64;  // sparse: the copy thread signals meta_ready without issuing the tcgen05.cp
+constexpr int kFlagEpiNoLoad = 256;   // sparse: the epilogue stores without reading tensor memory
+constexpr int kFlagEpiNoStore = 512;  // sparse: the epilogue reads tensor memory and stores nothing
+constexpr int kFlagEpiMathOnly = 2048; // sparse: the epilogue computes its results and stores none
+constexpr int kFlagClusterRelease = 65536;  // sparse: free the accumulator with a cluster-scope release (the earlier form)
 
 // kFlagProbe: [0] total clocks of the MMA thread's loop, [1] waiting for operands, [2] waiting for a
 // drained accumulator, [3] stages, [4] tiles
@@ -422,7 +428,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+            if (lane == 0) mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
         }
         if (lane == 0) tma_store_wait_all<0>();
     }
@@ -681,7 +687,8 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     const uint32_t sm = smem_u32(smem_stage + stage * Cfg::kStageBytes) + Cfg::kABytes +
                                         2 * Cfg::kBAtomBytes;
                     // two 16-byte columns of 128 rows -> 8 TMEM columns
-                    tmem_cp_128x256b_pair(tmem_meta + 8 * stage, make_desc_noswizzle(sm, 2048, 128));
+                    if ((flags & kFlagNoMetaCopy) == 0 || kb + (t - pair_id) < Cfg::kStages)
+                        tmem_cp_128x256b_pair(tmem_meta + 8 * stage, make_desc_noswizzle(sm, 2048, 128));
                     if (!mbar_wait(&bars.full[stage], phase, bars.abort_flag)) {
                         atomicExch(status, 406);
                         ok = false;
@@ -742,7 +749,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 if (ok) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                    if (lane == 0) mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
                 }
             }
         } else if (EPI == 1 && multi.count > 0 && multi.vec != 0) {
@@ -784,7 +791,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 if (ok) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                    if (lane == 0) mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
                 }
             }
         } else {
@@ -808,12 +815,30 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll 1
                 for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
                     const int m_first = m0 + c * 32;
-                    if (m_first >= M) break;
+                    if (m_first >= M || (flags & kFlagNoEpilogue) != 0) break;
                     uint32_t v[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    if ((flags & kFlagEpiNoLoad) == 0) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = (uint32_t)(j ^ lane);
+                    }
                     float as_lane = 0.f;
                     if (EPI == 1 && m_first + lane < M) as_lane = act_scale[m_first + lane];
-                    tmem_ld_wait();
+                    if ((flags & kFlagEpiNoLoad) == 0) tmem_ld_wait();
+                    if ((flags & kFlagEpiNoStore) != 0) continue;
+                    if ((flags & kFlagEpiMathOnly) != 0) {
+                        // the epilogue's arithmetic without its stores (one store that never happens)
+                        unsigned sum = 0;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float as = __shfl_sync(0xffffffffu, as_lane, j);
+                            sum += __half_as_ushort(__float2half_rn(
+                                dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias)));
+                        }
+                        if (sum == 0xfedcba98u) static_cast<unsigned*>(out)[n] = sum;
+                        continue;
+                    }
                     if (EPI == 1 && multi.count > 0)
                         store_transposed_chunk_multi(v, multi, N_out, M, n, m_first, as_lane, ws, bs, has_bias);
                     else
@@ -821,7 +846,13 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                if (lane == 0) {
+                    // CTA scope: the MMA thread consumes tensor memory (ordered by the tcgen05 fences),
+                    // not this warp's global stores - a cluster-scope release would first wait for
+                    // those to be acknowledged (measured 2 % of the kernel at 8192^3)
+                    if ((flags & kFlagClusterRelease) != 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                    else mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+                }
             }
         }
     }
@@ -1004,6 +1035,9 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     }
     if (BT == 224 && EPI == 1) {   // measurement variants exist for the default tile only
         FB200_SPARSE_VARIANT(1) FB200_SPARSE_VARIANT(2) FB200_SPARSE_VARIANT(3) FB200_SPARSE_VARIANT(4)
+        FB200_SPARSE_VARIANT(5) FB200_SPARSE_VARIANT(32) FB200_SPARSE_VARIANT(33) FB200_SPARSE_VARIANT(37)
+        FB200_SPARSE_VARIANT(65) FB200_SPARSE_VARIANT(256) FB200_SPARSE_VARIANT(512) FB200_SPARSE_VARIANT(2048)
+        FB200_SPARSE_VARIANT(65536)
     }
 #undef FB200_SPARSE_VARIANT
     return launch_pairs(sparse_pair_kernel<BT, EPI, 0>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w,

@@ -302,6 +302,13 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// Arrive on a barrier of another CTA of the cluster, ordering only this CTA's own earlier accesses
+// (CTA scope): enough when what the waiter consumes is tensor memory released by tcgen05 fences,
+// and it does not make the warp wait for its global stores to be acknowledged.
+__device__ __forceinline__ void mbar_arrive_remote_cta_scope(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
