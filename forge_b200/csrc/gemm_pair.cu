@@ -106,6 +106,7 @@ constexpr int kFlagNoMetaCopy = 64;  // sparse: the copy thread signals meta_rea
 constexpr int kFlagEpiNoLoad = 256;   // sparse: the epilogue stores without reading tensor memory
 constexpr int kFlagEpiNoStore = 512;  // sparse: the epilogue reads tensor memory and stores nothing
 constexpr int kFlagEpiMathOnly = 2048; // sparse: the epilogue computes its results and stores none
+constexpr int kFlagDirectStores = 128;   // sparse: the warps store the output themselves (the earlier epilogue)
 constexpr int kFlagClusterRelease = 65536;  // sparse: free the accumulator with a cluster-scope release (the earlier form)
 
 // kFlagProbe: [0] total clocks of the MMA thread's loop, [1] waiting for operands, [2] waiting for a
@@ -481,7 +482,8 @@ template <int BT, int EPI, int FLAGS>
 __global__ void __launch_bounds__(sp_threads(EPI), 1)
 sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_meta, const __grid_constant__ CUtensorMap tm_w2,
-                   const __grid_constant__ CUtensorMap tm_meta2, void* __restrict__ out, const OutDst multi,
+                   const __grid_constant__ CUtensorMap tm_meta2, const __grid_constant__ CUtensorMap tm_out,
+                   int out_tma, void* __restrict__ out, const OutDst multi,
                    const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                    const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
                    const __half* __restrict__ bias2, int M, int N_out, int K, int* __restrict__ status) {
@@ -794,6 +796,62 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     if (lane == 0) mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
                 }
             }
+        } else if (EPI == 1 && out_tma != 0 && (flags & kFlagDirectStores) == 0) {
+            // FP16 output through shared memory and TMA stores: each warp transposes its 32 tokens x 32
+            // columns into a 2 KB buffer (one 64-byte row per token) and one thread hands the box to the
+            // copy engine, which also clips it at the edges of the output. Stores issued by the warps
+            // themselves cost the tensor pipe 11 % of the kernel's time at 8192^3 (measured, whatever
+            // their width or cache policy).
+            uint8_t* stg = smem_tr + (warp_id - 2) * 2048;
+            const uint64_t store_policy = l2_policy_evict_first();
+            for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
+                const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
+                const int buf = (Cfg::kAccBufs == 2) ? (local & 1) : 0;
+                const uint32_t acc_phase = (Cfg::kAccBufs == 2) ? ((local >> 1) & 1) : (local & 1);
+                const int n_warp = tc.a_blk * 256 + (int)rank * 128 + q * 32;
+                const int n = n_warp + lane;
+                const int m0 = tc.b_blk * BT;
+                float ws = 0.f, bs = 0.f;
+                if (n < N_out) {
+                    ws = __half2float(w_scale[n]);
+                    if (has_bias) bs = __half2float(bias[n]);
+                }
+                if (!__all_sync(0xffffffffu, mbar_wait(&bars.tmem_full[buf], acc_phase, bars.abort_flag))) {
+                    atomicExch(status, 404);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BT;
+#pragma unroll 1
+                for (int c = chunk0; c < BT / 32; c += kSpEpiWarps / 4) {
+                    const int m_first = m0 + c * 32;
+                    if (m_first >= M || n_warp >= N_out || (flags & kFlagNoEpilogue) != 0) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    const float as_lane = (m_first + lane < M) ? act_scale[m_first + lane] : 0.f;
+                    if (lane == 0) tma_store_wait_read<0>();   // the previous box has left the buffer
+                    tmem_ld_wait();
+                    __syncwarp();
+                    // (16-byte staging stores after an 8 x 8 lane transpose were measured: slower, the
+                    // shuffles put the epilogue on the critical path of short-K shapes)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float as = __shfl_sync(0xffffffffu, as_lane, j);
+                        const float o = dequant_gemm(static_cast<int>(v[j]), mul_ftz(as, ws), bs, has_bias);
+                        *reinterpret_cast<__half*>(stg + j * 64 + lane * 2) = __float2half_rn(o);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d_hint(&tm_out, stg, n_warp, m_first, store_policy);
+                        tma_store_commit();
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote_cta_scope(mapa_shared(smem_u32(&bars.tmem_empty[buf]), 0));
+            }
+            if (lane == 0) tma_store_wait_all<0>();
         } else {
             for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
                 const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
@@ -1025,24 +1083,35 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     const long long tiles = (long long)((N_out + 2 * CTA_W - 1) / (2 * CTA_W)) * ((M + BT - 1) / BT);
     OutDst md = {};
     if (multi != nullptr) md = *multi;
+    // FP16 output as 32-token x 32-column boxes for the TMA-store epilogue (single destination only)
+    CUtensorMap tm_out = tm_x;
+    int out_tma = 0;
+    if (EPI == 1 && multi == nullptr && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const uint64_t dims[2] = {(uint64_t)N_out, (uint64_t)M};
+        const uint64_t str[1] = {(uint64_t)N_out * 2};
+        const uint32_t box[2] = {32, 32};
+        if (!make_tmap(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return kLaunchFailed;
+        out_tma = 1;
+    }
     const int flags = tuning_knob(kKnobPairFlags);
 #define FB200_SPARSE_VARIANT(F)                                                                                       \
     if (flags == F) {                                                                                                 \
         static int mp[64] = {};                                                                                       \
         return launch_pairs(sparse_pair_kernel<BT, EPI, F>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, mp, tm_w, tm_x, \
-                            tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, \
+                            tm_meta, tm_w2, tm_meta2, tm_out, out_tma, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, \
                             status);                                                                                  \
     }
     if (BT == 224 && EPI == 1) {   // measurement variants exist for the default tile only
         FB200_SPARSE_VARIANT(1) FB200_SPARSE_VARIANT(2) FB200_SPARSE_VARIANT(3) FB200_SPARSE_VARIANT(4)
         FB200_SPARSE_VARIANT(5) FB200_SPARSE_VARIANT(32) FB200_SPARSE_VARIANT(33) FB200_SPARSE_VARIANT(37)
         FB200_SPARSE_VARIANT(65) FB200_SPARSE_VARIANT(256) FB200_SPARSE_VARIANT(512) FB200_SPARSE_VARIANT(2048)
-        FB200_SPARSE_VARIANT(65536)
+        FB200_SPARSE_VARIANT(65536) FB200_SPARSE_VARIANT(128)
     }
 #undef FB200_SPARSE_VARIANT
     return launch_pairs(sparse_pair_kernel<BT, EPI, 0>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w,
-                        tm_x, tm_meta, tm_w2, tm_meta2, out, md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K,
-                        status);
+                        tm_x, tm_meta, tm_w2, tm_meta2, tm_out, out_tma, out, md, act_scale, w_scale, bias, w_scale2, bias2,
+                        M, N_out, K, status);
 }
 
 template <int EPI>
