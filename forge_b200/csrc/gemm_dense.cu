@@ -489,6 +489,14 @@ int dense_gemm_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const 
     // TMA path only: K a multiple of 16, N a multiple of 8, 16-byte aligned operands
     if (K % 16 != 0 || N % 8 != 0 || !aligned16(A) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(out))
         return kBadShape;
+    // CTA-pair kernel (256 tokens x 128 output columns per pair of SMs; dense tile knob 512 forces it, any other
+    // forced tile keeps the single-CTA kernel) once every pair has a tile
+    const int force_bn = tuning_knob(kKnobDenseTile);
+    const long long pair_tiles = (long long)((M + 255) / 256) * ((N + 127) / 128);
+    if (force_bn == 512 || (force_bn == 0 && pair_tiles >= sm_count() / 2 && K >= 512)) {
+        const int r = dense_pair_gated(A, Wg, Wu, act_scale, wg_scale, wu_scale, bg, bu, out, M, K, N, stream);
+        if (r >= 0) return r;
+    }
     return launch_dense<256, 2>(A, Wg, act_scale, wg_scale, bg, out, M, K, N, stream, Wu, wu_scale, bu);
 }
 

@@ -192,11 +192,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_b_half, const __grid_constant__ CUtensorMap tm_c,
                   const float* __restrict__ act_scale,
-                  const __half* __restrict__ w_scale, const __half* __restrict__ bias, int M, int N, int K,
+                  const __half* __restrict__ w_scale, const __half* __restrict__ bias,
+                  const __half* __restrict__ w_scale2, const __half* __restrict__ bias2, int M, int N, int K,
                   int* __restrict__ status) {
+    // EPI 2 (gated): the pair's B tile is 128 rows of the gate weight (staged by CTA 0, map tm_b)
+    // followed by the same 128 rows of the up weight (staged by CTA 1, map tm_b_half), so every
+    // accumulator row holds gate and up of 128 output columns and the epilogue writes
+    // SiLU(gate) * up for a 256 x 128 output tile. N counts output columns.
     using Cfg = DensePairCfg;
-    constexpr int flags = FLAGS;
+    constexpr int flags = FLAGS | (EPI == 2 ? kFlagNoSplit : 0);
     constexpr int BN = 256;
+    constexpr int TILE_N = (EPI == 2) ? BN / 2 : BN;   // output columns per tile
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* smem_ab = smem;
     uint8_t* smem_epi = smem + Cfg::kStages * Cfg::kStageBytes;
@@ -214,7 +220,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
 
     const int m_blocks = (M + 255) / 256;
-    const int n_blocks = (N + 255) / 256;
+    const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const int num_kb = (K + 127) / 128;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
@@ -267,13 +273,16 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         if (leader)
                             mbar_expect_tx(&bars.full[stage], 2 * (Cfg::kABytes + (half ? Cfg::kBBytes / 2 : Cfg::kBBytes)));
                         tma_load_2d_pair(sa, &tm_a, full_leader, kb * 128, tc.a_blk * 256 + (int)rank * 128);
-                        if (one_producer) {
+                        if (one_producer && EPI != 2) {
                             if (half)
                                 tma_load_2d_pair(sb, &tm_b_half, full_leader, kb * 128,
                                                  tc.b_blk * 256 + item.n_off + (int)rank * 64);
                             else
                                 tma_load_2d_pair(sb, &tm_b, full_leader, kb * 128, tc.b_blk * 256 + (int)rank * 128);
                         }
+                    } else if (EPI == 2) {
+                        // CTA 0: 128 gate rows, CTA 1: the same rows of the up weight
+                        tma_load_2d_pair(sb, leader ? &tm_b : &tm_b_half, full_leader, kb * 128, tc.b_blk * TILE_N);
                     } else if (half) {
                         // each CTA stages 64 of the 128 B rows of a half tile
                         tma_load_2d_pair(sb, &tm_b_half, full_leader, kb * 128,
@@ -358,16 +367,23 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row0 = tc.a_blk * 256 + (int)rank * 128;
             const int row = row0 + q * 32 + lane;
-            const int n0 = tc.b_blk * BN + item.n_off;
+            const int n0 = tc.b_blk * TILE_N + item.n_off;
+            // EPI 1: [w_scale BN][bias BN]; EPI 2: [gate scale][gate bias][up scale][up bias], TILE_N each
             __half* s_ws = smem_scale + buf * 2 * BN;
-            __half* s_bias = s_ws + BN;
+            __half* s_bias = s_ws + TILE_N;
+            __half* s_ws2 = s_bias + TILE_N;
+            __half* s_bias2 = s_ws2 + TILE_N;
             float as = 0.f;
-            if (EPI == 1) {
+            if (EPI != 0) {
                 if (ok) {
-                    for (int i = epi_tid; i < BN; i += kEpiThreads) {
+                    for (int i = epi_tid; i < TILE_N; i += kEpiThreads) {
                         const int n = n0 + i;
                         s_ws[i] = (n < N) ? w_scale[n] : __float2half(0.f);
                         s_bias[i] = (has_bias && n < N) ? bias[n] : __float2half(0.f);
+                        if (EPI == 2) {
+                            s_ws2[i] = (n < N) ? w_scale2[n] : __float2half(0.f);
+                            s_bias2[i] = (bias2 != nullptr && n < N) ? bias2[n] : __float2half(0.f);
+                        }
                     }
                     as = (row < M) ? act_scale[row] : 0.f;
                 }
@@ -381,11 +397,37 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < item.n_cols / CH; c++) {
+            for (int c = 0; c < (EPI == 2 ? TILE_N : item.n_cols) / CH; c++) {
                 uint32_t packed[32];
                 if (EPI == 0) {
                     tmem_ld_32x32b_x32(taddr + c * CH, packed);
                     tmem_ld_wait();
+                } else if (EPI == 2) {
+                    const bool has_bias2 = (bias2 != nullptr);
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {   // two 32-column halves of the 64-column staged row
+                        uint32_t vg[32], vu[32];
+                        const int col = c * CH + hh * 32;
+                        tmem_ld_32x32b_x32(taddr + col, vg);
+                        tmem_ld_32x32b_x32(taddr + TILE_N + col, vu);
+                        tmem_ld_wait();
+                        const __half2* gs2 = reinterpret_cast<const __half2*>(s_ws + col);
+                        const __half2* gb2 = reinterpret_cast<const __half2*>(s_bias + col);
+                        const __half2* us2 = reinterpret_cast<const __half2*>(s_ws2 + col);
+                        const __half2* ub2 = reinterpret_cast<const __half2*>(s_bias2 + col);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const float2 gw = __half22float2(gs2[i]), gb = __half22float2(gb2[i]);
+                            const float2 uw = __half22float2(us2[i]), ub = __half22float2(ub2[i]);
+                            const float g0 = dequant_gemm(static_cast<int>(vg[2 * i]), mul_ftz(as, gw.x), gb.x, has_bias);
+                            const float g1 =
+                                dequant_gemm(static_cast<int>(vg[2 * i + 1]), mul_ftz(as, gw.y), gb.y, has_bias);
+                            const float u0 = dequant_gemm(static_cast<int>(vu[2 * i]), mul_ftz(as, uw.x), ub.x, has_bias2);
+                            const float u1 =
+                                dequant_gemm(static_cast<int>(vu[2 * i + 1]), mul_ftz(as, uw.y), ub.y, has_bias2);
+                            packed[hh * 16 + i] = pack_half2(silu_mul(g0, u0), silu_mul(g1, u1));
+                        }
+                    }
                 } else {
                     uint32_t va[32], vb[32];
                     tmem_ld_32x32b_x32(taddr + c * CH, va);
@@ -976,7 +1018,8 @@ int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaSt
 
 template <int EPI>
 int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
-                      const __half* bias, void* out, int M, int K, int N, cudaStream_t stream) {
+                      const __half* bias, void* out, int M, int K, int N, cudaStream_t stream,
+                      const int8_t* B2 = nullptr, const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
     static int max_pairs[64] = {};
     CUtensorMap tm_a, tm_b, tm_b_half, tm_c;
     {
@@ -996,8 +1039,10 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
         const uint64_t str[1] = {(uint64_t)K};
-        const uint32_t box[2] = {128, 64};
-        if (!make_tmap(&tm_b_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        // EPI 0/1: 64-row boxes for the halves of a split tile; EPI 2: the up weight, whole 128-row slabs
+        const uint32_t box[2] = {128, (uint32_t)((EPI == 2) ? 128 : 64)};
+        if (!make_tmap(&tm_b_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (EPI == 2) ? B2 : B, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
     }
     {
@@ -1010,17 +1055,24 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     }
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
-    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-    const int flags = tuning_knob(kKnobPairFlags);
+    constexpr int TILE_N = (EPI == 2) ? 128 : 256;
+    const long long tiles = (long long)((M + 255) / 256) * ((N + TILE_N - 1) / TILE_N);
+    const int flags = (EPI == 2) ? 0 : tuning_knob(kKnobPairFlags);
 #define FB200_DENSE_VARIANT(F)                                                                                        \
     if (flags == F) {                                                                                                 \
         static int mp[64] = {};                                                                                       \
         return launch_pairs(dense_pair_kernel<EPI, F>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, mp, tm_a, tm_b, \
-                            tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);                              \
+                            tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, status);             \
     }
-    FB200_DENSE_VARIANT(1) FB200_DENSE_VARIANT(2) FB200_DENSE_VARIANT(3) FB200_DENSE_VARIANT(8) FB200_DENSE_VARIANT(16)
-    FB200_DENSE_VARIANT(18)
+    if constexpr (EPI != 2) {
+        FB200_DENSE_VARIANT(1) FB200_DENSE_VARIANT(2) FB200_DENSE_VARIANT(3) FB200_DENSE_VARIANT(8)
+        FB200_DENSE_VARIANT(16) FB200_DENSE_VARIANT(18)
+    }
 #undef FB200_DENSE_VARIANT
+    if constexpr (EPI == 2)
+        return launch_pairs(dense_pair_kernel<2, kFlagNoSplit>, kThreads, DensePairCfg::kSmemBytes, tiles, stream,
+                            max_pairs, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K,
+                            status);
     // The half-tile bookkeeping costs about 2 % where no tile is ever cut (8192^3): the instantiation
     // without it runs unless this launch's last wave will be split.
     {
@@ -1034,10 +1086,11 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
         const bool will_split = pairs > 0 && dense_work((int)tiles, pairs, true).items != (int)tiles;
         if (!will_split && pairs > 0)
             return launch_pairs(dense_pair_kernel<EPI, kFlagNoSplit>, kThreads, DensePairCfg::kSmemBytes, tiles, stream,
-                                mp_probe, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);
+                                mp_probe, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K,
+                                status);
     }
     return launch_pairs(dense_pair_kernel<EPI, 0>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b,
-                        tm_b_half, tm_c, act_scale, w_scale, bias, M, N, K, status);
+                        tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, status);
 }
 
 template <int BT, int EPI>
@@ -1140,6 +1193,12 @@ int dense_pair_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K,
 int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream) {
     return launch_dense_pair<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+}
+
+int dense_pair_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                     const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,
+                     int M, int K, int N, cudaStream_t stream) {
+    return launch_dense_pair<2>(A, Wg, act_scale, wg_scale, bg, out, M, K, N, stream, Wu, wu_scale, bu);
 }
 
 int sparse_pair_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,

@@ -12,6 +12,11 @@ int dense_pair_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K,
 int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream);
 
+// out[m][n] = SiLU(gate) * up of the two dequantised products, N output columns (256 x 128 per pair tile).
+int dense_pair_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
+                     const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,
+                     int M, int K, int N, cudaStream_t stream);
+
 // bt: tokens per pair tile, one of 128, 192, 224, 256.
 int sparse_pair_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,
                     int N_out, cudaStream_t stream, int bt);
@@ -19,7 +24,7 @@ int sparse_pair_dequant(const int8_t* W_comp, const int8_t* x, const uint32_t* w
                         const __half* w_scale, const __half* bias, __half* out, int M, int K, int N_out,
                         cudaStream_t stream, int bt);
 
-// Copies the sparse pair kernel's probe counters (pair-kernel flag 32) to `out`.
+// Copies the sparse pair kernel's probe counters (pair-kernel flag 4) to `out`.
 int read_pair_probe(unsigned long long* out, int n);
 
 struct OutDst;

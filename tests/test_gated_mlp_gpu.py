@@ -84,6 +84,14 @@ def test_gated_gemm_dense_and_sparse(M, K, N, with_bias):
                             sg.numpy(), su.numpy(), None if bg is None else bg.numpy(),
                             None if bu is None else bu.numpy())
     assert O.half_ulp_distance(h.cpu().numpy(), want).max() <= 1
+    # the CTA-pair form of the gated kernel (tile id 512) must give the same bits as the single-CTA one
+    _lib.load().forge_b200_set_dense_tile(512)
+    try:
+        h_pair = _gated_dense(dxq, dxs, d(Wg), d(Wu), dsg, dsu, dbg, dbu)
+        _status_ok()
+    finally:
+        _lib.load().forge_b200_set_dense_tile(0)
+    assert torch.equal(h_pair.view(torch.int16), h.view(torch.int16))
     # sparse: vs the oracle on the pruned weights, and bit-identical to the dense kernel on them
     cg, mg = _compress(Wg)
     cu, mu = _compress(Wu)
