@@ -103,9 +103,9 @@ constexpr int kFlagNoSplit = 8;     // dense: never cut the last wave's tiles in
 constexpr int kFlagOneProducer = 16; // dense: warp 0 issues both TMA loads of a stage, the second producer idles
 constexpr int kFlagNoEpilogue = 32;  // sparse: the epilogue warps free the accumulator without reading or storing it
 constexpr int kFlagNoMetaCopy = 64;  // sparse: the copy thread signals meta_ready without issuing the tcgen05.cp
-constexpr int kFlagEpiNoLoad = 256;   // sparse: the epilogue stores without reading tensor memory
-constexpr int kFlagEpiNoStore = 512;  // sparse: the epilogue reads tensor memory and stores nothing
-constexpr int kFlagEpiMathOnly = 2048; // sparse: the epilogue computes its results and stores none
+constexpr int kFlagEpiNoLoad = 256;   // sparse, with 128: the epilogue stores without reading tensor memory
+constexpr int kFlagEpiNoStore = 512;  // sparse, with 128: the epilogue reads tensor memory and stores nothing
+constexpr int kFlagEpiMathOnly = 2048; // sparse, with 128: the epilogue computes its results and stores none
 constexpr int kFlagDirectStores = 128;   // sparse: the warps store the output themselves (the earlier epilogue)
 constexpr int kFlagClusterRelease = 65536;  // sparse: free the accumulator with a cluster-scope release (the earlier form)
 
@@ -1158,8 +1158,9 @@ int launch_sparse_pair(const int8_t* W_comp, const int8_t* x, const uint32_t* w_
     if (BT == 224 && EPI == 1) {   // measurement variants exist for the default tile only
         FB200_SPARSE_VARIANT(1) FB200_SPARSE_VARIANT(2) FB200_SPARSE_VARIANT(3) FB200_SPARSE_VARIANT(4)
         FB200_SPARSE_VARIANT(5) FB200_SPARSE_VARIANT(32) FB200_SPARSE_VARIANT(33) FB200_SPARSE_VARIANT(37)
-        FB200_SPARSE_VARIANT(65) FB200_SPARSE_VARIANT(256) FB200_SPARSE_VARIANT(512) FB200_SPARSE_VARIANT(2048)
-        FB200_SPARSE_VARIANT(65536) FB200_SPARSE_VARIANT(128)
+        FB200_SPARSE_VARIANT(65) FB200_SPARSE_VARIANT(65536) FB200_SPARSE_VARIANT(128)
+        // the three splits of the direct-store epilogue (128 + 256 / 512 / 2048)
+        FB200_SPARSE_VARIANT(384) FB200_SPARSE_VARIANT(640) FB200_SPARSE_VARIANT(2176)
     }
 #undef FB200_SPARSE_VARIANT
     return launch_pairs(sparse_pair_kernel<BT, EPI, 0>, sp_threads(EPI), Cfg::kSmemBytes, tiles, stream, max_pairs, tm_w,
