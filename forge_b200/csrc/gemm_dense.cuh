@@ -38,6 +38,7 @@ enum TuningKnob : int {
     kKnobLastPairs = 4,        // written by the launcher: CTA pairs of the last pair-kernel launch
     kKnobGemvVariant = 5,      // 1-4 token sparse kernel: 1 = token slices in registers, 2 = in shared memory
     kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)
+    kKnobDenseBand = 7,        // dense CTA-pair kernel: 256-row blocks per raster band
 };
 int tuning_knob(int key);
 void set_tuning_knob(int key, int value);

@@ -194,7 +194,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   const float* __restrict__ act_scale,
                   const __half* __restrict__ w_scale, const __half* __restrict__ bias,
                   const __half* __restrict__ w_scale2, const __half* __restrict__ bias2, int M, int N, int K,
-                  int* __restrict__ status) {
+                  int band, int* __restrict__ status) {
     // EPI 2 (gated): the pair's B tile is 128 rows of the gate weight (staged by CTA 0, map tm_b)
     // followed by the same 128 rows of the up weight (staged by CTA 1, map tm_b_half), so every
     // accumulator row holds gate and up of 128 output columns and the epilogue writes
@@ -256,7 +256,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             int it = 0;
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const DenseItem item = dense_item(t, work);
-                const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, kDenseBand);
+                const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, band);
                 const bool half = item.n_cols == 128;
                 for (int kb = 0; kb < num_kb; kb++, it++) {
                     if (!mbar_wait(&bars.empty[stage], phase ^ 1, bars.abort_flag)) {
@@ -362,7 +362,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         bool ok = true;
         for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
             const DenseItem item = dense_item(t, work);
-            const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, kDenseBand);
+            const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, band);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             const int row0 = tc.a_blk * 256 + (int)rank * 128;
@@ -1056,13 +1056,17 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     int* status = status_word();
     if (status == nullptr) return kLaunchFailed;
     constexpr int TILE_N = (EPI == 2) ? 128 : 256;
+    // a band's rows of A are re-read from L2 by every wave and should stay there: 16 blocks up to
+    // K = 8192, 8 beyond (K = 14336: 584 -> less DRAM read per launch, 1 % faster; 8 at K = 8192: 1 % slower)
+    const int band = tuning_knob(kKnobDenseBand) > 0 ? tuning_knob(kKnobDenseBand)
+                                                     : ((long long)kDenseBand * 256 * K > (40ll << 20) ? kDenseBand / 2 : kDenseBand);
     const long long tiles = (long long)((M + 255) / 256) * ((N + TILE_N - 1) / TILE_N);
     const int flags = (EPI == 2) ? 0 : tuning_knob(kKnobPairFlags);
 #define FB200_DENSE_VARIANT(F)                                                                                        \
     if (flags == F) {                                                                                                 \
         static int mp[64] = {};                                                                                       \
         return launch_pairs(dense_pair_kernel<EPI, F>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, mp, tm_a, tm_b, \
-                            tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, status);             \
+                            tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, band, status);       \
     }
     if constexpr (EPI != 2) {
         FB200_DENSE_VARIANT(1) FB200_DENSE_VARIANT(2) FB200_DENSE_VARIANT(3) FB200_DENSE_VARIANT(8)
@@ -1072,7 +1076,7 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
     if constexpr (EPI == 2)
         return launch_pairs(dense_pair_kernel<2, kFlagNoSplit>, kThreads, DensePairCfg::kSmemBytes, tiles, stream,
                             max_pairs, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K,
-                            status);
+                            band, status);
     // The half-tile bookkeeping costs about 2 % where no tile is ever cut (8192^3): the instantiation
     // without it runs unless this launch's last wave will be split.
     {
@@ -1087,10 +1091,10 @@ int launch_dense_pair(const int8_t* A, const int8_t* B, const float* act_scale, 
         if (!will_split && pairs > 0)
             return launch_pairs(dense_pair_kernel<EPI, kFlagNoSplit>, kThreads, DensePairCfg::kSmemBytes, tiles, stream,
                                 mp_probe, tm_a, tm_b, tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K,
-                                status);
+                                band, status);
     }
     return launch_pairs(dense_pair_kernel<EPI, 0>, kThreads, DensePairCfg::kSmemBytes, tiles, stream, max_pairs, tm_a, tm_b,
-                        tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, status);
+                        tm_b_half, tm_c, act_scale, w_scale, bias, w_scale2, bias2, M, N, K, band, status);
 }
 
 template <int BT, int EPI>

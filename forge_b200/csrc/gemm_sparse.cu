@@ -501,20 +501,19 @@ int sparse_dispatch(const int8_t* W_comp, const int8_t* x, const uint32_t* w_met
 // (src/gemm/int8_sparse.cu:885-920, fitted there to an RTX 4090): a launch of variant v costs
 //     c0_v + waves_v * (a_v * ksteps + b_v)   microseconds,
 // waves_v = ceil(tiles_v / co-resident tiles), ksteps = ceil(K / 256). The constants are a
-// non-negative least-squares fit to single launches with cold L2 on a B200 over the reference's
+// non-negative least-squares fit (relative errors) to single launches with cold L2 on a B200 over the reference's
 // benchmark grid ((K, N) in {(1536,6144), (6144,1536), (1280,5120), (5120,1280)} x M in {64, 1024, 4096,
 // 8192}), the 11008 x 4096 weight at M = 8 ... 8192, the 4096 <-> 14336 and 8192 -> 28672 layers at
-// M = 8192 and four square shapes; on those 36 points the model's pick is within 6 % of the best
-// measured variant everywhere (sum of times 2743 us against 2740 us for the per-point best and 2836 us
-// for the rule it replaces).
+// M = 8192 and four square shapes; on those points the model's pick is the best measured variant or
+// within 0.3 % of it (sum of times 2581 us, the same as the per-point best).
 struct TileCost {
     int bt;
     bool pair;
     float c0, a, b;
 };
 constexpr TileCost kTileCosts[] = {
-    {32, false, 11.24f, 0.273f, 0.261f},  {64, false, 11.10f, 0.291f, 0.347f}, {128, false, 13.47f, 0.410f, 0.550f},
-    {192, true, 15.61f, 0.440f, 0.994f}, {224, true, 15.56f, 0.488f, 1.091f},
+    {32, false, 9.82f, 0.271f, 0.349f},  {64, false, 10.60f, 0.281f, 0.421f}, {128, false, 10.50f, 0.410f, 0.800f},
+    {192, true, 12.18f, 0.417f, 0.938f}, {224, true, 11.64f, 0.447f, 1.276f},
 };
 
 // force_bt: 0 = free choice; 1 = one CTA per tile, 32 or 64 tokens; 32 / 64 / 128 = that single-CTA tile;
