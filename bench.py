@@ -934,7 +934,8 @@ def main():
     ap.add_argument("--graph", type=int, default=0, help="--case runs: capture --reps calls in a CUDA graph and time replays")
     ap.add_argument("--knob", action="append", default=[],
                     help="--case runs: library-internal tuning knob as key=value (2 = cap on CTA pairs, 3 = pair-kernel "
-                         "flags: 1 operands resident after the first ring fill, 2 one commit per CTA, 4 probe)")
+                         "measurement variant: 1 operands resident after the first ring fill, 4 clock probe, 32 no epilogue, "
+                         "128 stores issued by the epilogue warps ...; 7 = dense raster band)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"],
                     help="shard_cols: all-gather by the GEMM epilogue's peer stores (fused) or by NCCL")
     ap.add_argument("--flush-l2", type=int, default=1, help="write 256 MiB between launches of a --case run")

@@ -31,10 +31,10 @@ enum TuningKnob : int {
     kKnobDenseTile = 0,        // pinned dense tile width
     kKnobSparseTile = 1,       // pinned sparse token-tile width
     kKnobMaxPairs = 2,         // CTA-pair kernels: launch at most this many pairs
-    kKnobPairFlags = 3,        // CTA-pair kernels, measurement only: bit 0 = operands stay resident after the
-                               // first ring fill (wrong results; tensor-core side alone), bit 1 = one commit
-                               // per CTA to free a stage, bit 2 = sparse MMA thread records its wait clocks,
-                               // bit 3 = dense: no half tiles in the last wave
+    kKnobPairFlags = 3,        // CTA-pair kernels, measurement only: selects one of the instantiated variants
+                               // (flag values kFlag... in gemm_pair.cu; e.g. 1 = operands stay resident after
+                               // the first ring fill - wrong results, tensor-core side alone - 4 = the sparse
+                               // MMA thread records its wait clocks, 128 = stores issued by the epilogue warps)
     kKnobLastPairs = 4,        // written by the launcher: CTA pairs of the last pair-kernel launch
     kKnobGemvVariant = 5,      // 1-4 token sparse kernel: 1 = token slices in registers, 2 = in shared memory
     kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)

@@ -20,7 +20,7 @@ void forge_b200_set_sparse_tile(int bt);
 void forge_b200_set_tuning(int key, int value);
 int forge_b200_get_tuning(int key);
 
-/* Copies up to 8 probe counters of the sparse CTA-pair kernel (pair-kernel flag 32) to out. */
+/* Copies up to 8 probe counters of the sparse CTA-pair kernel (pair-kernel flag 4) to out. */
 int forge_b200_read_probe(unsigned long long* out, int n);
 
 /* Ceiling probes (probes.cu). mma_rate: clocks per tcgen05.mma kind::i8 instruction with operands
