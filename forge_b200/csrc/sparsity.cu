@@ -39,6 +39,33 @@ __device__ __forceinline__ uint32_t prune_group(uint32_t w, uint32_t& kept) {
     return (uint32_t)(p0 | (p1 << 2));
 }
 
+// Two groups at once (wA, wB): the same decision with the keys of both groups in the two 16-bit
+// lanes of a register, so that every min / max of the network serves two groups, and with the
+// surviving bytes picked by one PRMT whose selector is computed (no variable shifts, no bit
+// scans). The kernel is bound by the integer ALU pipe (92 % busy with prune_group), not by HBM.
+// `comp` receives the compressed word of both groups (A in the low half), the return value holds
+// the two nibbles in its 16-bit lanes.
+__device__ __forceinline__ uint32_t prune_pair(uint32_t wA, uint32_t wB, uint32_t& comp) {
+    const uint32_t aA = __vabs4(wA), aB = __vabs4(wB);
+    // key_i = (|x_i| << 2) | i, lane 0: group A, lane 1: group B
+    const uint32_t k0 = (__byte_perm(aA, aB, 0x4400) & 0x00FF00FFu) * 4u;
+    const uint32_t k1 = (__byte_perm(aA, aB, 0x5511) & 0x00FF00FFu) * 4u + 0x00010001u;
+    const uint32_t k2 = (__byte_perm(aA, aB, 0x6622) & 0x00FF00FFu) * 4u + 0x00020002u;
+    const uint32_t k3 = (__byte_perm(aA, aB, 0x7733) & 0x00FF00FFu) * 4u + 0x00030003u;
+    const uint32_t lo01 = __vminu2(k0, k1), hi01 = __vmaxu2(k0, k1);
+    const uint32_t lo23 = __vminu2(k2, k3), hi23 = __vmaxu2(k2, k3);
+    const uint32_t h1 = __vmaxu2(hi01, hi23);                                   // largest key
+    const uint32_t h2 = __vimax3_u16x2(__vminu2(hi01, hi23), lo01, lo23);       // second largest
+    const uint32_t pa = h1 & 0x00030003u, pb = h2 & 0x00030003u;                // the two kept positions
+    const uint32_t p0 = __vminu2(pa, pb), p1 = __vmaxu2(pa, pb);
+    // PRMT selector per lane: byte 0 <- position p0, byte 1 <- position p1, bytes 2, 3 <- zero
+    const uint32_t sel = p1 * 16u + p0 + 0x44004400u;
+    const uint32_t keptA = __byte_perm(wA, 0u, sel);
+    const uint32_t keptB = __byte_perm(wB, 0u, sel >> 16);
+    comp = __byte_perm(keptA, keptB, 0x5410);
+    return p1 * 4u + p0;
+}
+
 }  // namespace fb200
 
 // Public kernel declarations of the reference headers (include/forge/sparsity/prune_compress.cuh:16-21,
@@ -104,18 +131,11 @@ prune_compress_vec_kernel(const uint4* __restrict__ weight, uint2* __restrict__ 
     for (int u = 0; u < 4; u++) {
         const long long p = first + u * 256;
         if (p >= npieces) break;
-        const uint32_t g4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-        uint32_t comp[2] = {0u, 0u};
-        uint32_t meta = 0u;
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-            uint32_t kept;
-            const uint32_t nib = prune_group(g4[g], kept);
-            comp[g >> 1] |= kept << (16 * (g & 1));
-            meta |= nib << (8 * g);
-        }
+        uint32_t comp[2];
+        const uint32_t nib01 = prune_pair(w[u].x, w[u].y, comp[0]);
+        const uint32_t nib23 = prune_pair(w[u].z, w[u].w, comp[1]);
         __stcs(compressed + p, make_uint2(comp[0], comp[1]));
-        __stcs(metadata_raw + p, meta);
+        __stcs(metadata_raw + p, __byte_perm(nib01, nib23, 0x6420));   // one nibble byte per group
     }
 }
 
@@ -196,14 +216,12 @@ prepare_weight_kernel(const T* __restrict__ w, int8_t* __restrict__ w_int8, int8
             d[1] = make_uint4(q[4], q[5], q[6], q[7]);
         }
         if (W_comp != nullptr) {
-            uint32_t comp[4] = {0u, 0u, 0u, 0u};
+            uint32_t comp[4];
             uint32_t meta = 0;
 #pragma unroll
-            for (int g = 0; g < 8; g++) {
-                uint32_t kept;
-                const uint32_t nib = prune_group(q[g], kept);
-                comp[g >> 1] |= kept << (16 * (g & 1));
-                meta |= nib << (4 * g);
+            for (int g = 0; g < 4; g++) {
+                const uint32_t nib2 = prune_pair(q[2 * g], q[2 * g + 1], comp[g]);
+                meta |= ((nib2 & 0xFu) | ((nib2 >> 12) & 0xF0u)) << (8 * g);   // nibbles 2g and 2g+1
             }
             *reinterpret_cast<uint4*>(W_comp + (size_t)row * (K / 2) + c * 16) =
                 make_uint4(comp[0], comp[1], comp[2], comp[3]);
