@@ -158,14 +158,10 @@ pack_metadata_vec_kernel(const uint4* __restrict__ meta_raw, uint2* __restrict__
         uint32_t out[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            uint32_t pk = 0;
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const uint32_t x = w[2 * h + j] & 0x0F0F0F0Fu;   // four nibbles, one per byte
-                const uint32_t four = (x & 0xF) | ((x >> 4) & 0xF0) | ((x >> 8) & 0xF00) | ((x >> 12) & 0xF000);
-                pk |= four << (16 * j);
-            }
-            out[h] = pk;
+            // four nibbles, one per byte -> neighbours merged into bytes 0 and 2 -> one PRMT gathers
+            // those bytes of both words: eight nibbles in order
+            const uint32_t xa = w[2 * h] & 0x0F0F0F0Fu, xb = w[2 * h + 1] & 0x0F0F0F0Fu;
+            out[h] = __byte_perm(xa | (xa >> 4), xb | (xb >> 4), 0x6420);
         }
         __stcs(meta_packed + p, make_uint2(out[0], out[1]));
     }
