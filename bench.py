@@ -509,6 +509,19 @@ def _build_case(name, args, lib, C, dev, g, S):
         else:
             fn = lambda: lib.forge_int8_gemm_s32(x.data_ptr(), W.data_ptr(), out.data_ptr(), m, k, n, S[0])
         shape = {"M": m, "N": n, "K": k}
+    elif name == "linear":
+        # the W8A8 linear call itself (per-token quantize + dense GEMM + dequant + bias); default = config 2
+        m, n, k = args.m or 4096, args.n or 4096, args.k or 4096
+        x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
+        W = ri8(n, k)
+        w_s = (torch.rand(n, generator=g, device=dev) * 0.02 + 0.001).half()
+        bias = (torch.randn(n, generator=g, device=dev) * 0.01).half()
+        q = torch.empty((m, k), dtype=torch.int8, device=dev)
+        sc = torch.empty((m,), dtype=torch.float32, device=dev)
+        out = torch.empty((m, n), dtype=torch.float16, device=dev)
+        fn = lambda: lib.forge_int8_linear(x.data_ptr(), W.data_ptr(), w_s.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                           m, k, n, q.data_ptr(), sc.data_ptr(), S[0])
+        work, unit, bound, shape = 2.0 * m * n * k / 1e12, "TOP/s", "tensor", {"M": m, "N": n, "K": k}
     elif name == "quantize":
         m, k = args.m or 16384, args.k or 8192
         x = torch.randn((m, k), generator=g, device=dev, dtype=torch.float16)
@@ -913,7 +926,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--case", default="headline",
                     help="headline (the contract line) or one kernel: dense, dense_s32, sparse, sparse_s32, "
-                         "quantize, dequant, prune, pack, conv, conv_transpose, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn); "
+                         "linear, quantize, dequant, prune, pack, conv, conv_transpose, mlp, mlp_sparse (for mlp: --m tokens --k d_model --n d_ffn); "
                          "under torchrun: shard_rows, shard_cols, shard_mlp, shard_mlp_sparse")
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)

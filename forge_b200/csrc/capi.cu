@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "conv.cuh"
 #include "gemm_dense.cuh"
+#include "gemm_pair.cuh"
 #include "gemm_sparse.cuh"
 #include "gemm_fq.cuh"
 #include "kernels.cuh"
@@ -84,6 +85,7 @@ int forge_int8_linear(const void* x, const int8_t* w_int8, const void* w_scale, 
     if (M <= 0 || K <= 0 || N <= 0) return kOk;
     const int r = quantize_activation(H(x), scratch_a_int8, scratch_a_scale, M, K, S(stream));
     if (r != kOk) return r;
+    const BehindQuantizer dependent;
     return dense_gemm_dequant(scratch_a_int8, w_int8, scratch_a_scale, H(w_scale), H(bias), H(output), M, K, N,
                               S(stream), force_dense_bn());
 }
@@ -163,6 +165,7 @@ int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t
     if (scratch_x_int8 == nullptr || scratch_x_scale == nullptr) return kBadPointer;
     const int r = quantize_activation(H(x), scratch_x_int8, scratch_x_scale, M, K, S(stream));
     if (r != kOk) return r;
+    const BehindQuantizer dependent;
     return forge_sparse_int8_gemm(W_comp, scratch_x_int8, w_meta, scratch_x_scale, w_scale, bias, output, M, K, N_out,
                                   splitk_workspace, split_k, stream, FORGE_SPARSE_TILE_AUTO);
 }
@@ -250,11 +253,14 @@ int forge_w8a8_gated_mlp(const void* x, const int8_t* Wg, const int8_t* Wu, cons
     const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
     int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
     if (r != kOk) return r;
+    pair_launch_behind_quantizer(true);
     r = dense_gemm_gated(w.xq, Wg, Wu, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h, M, d_model, d_ffn,
                          S(stream));
+    pair_launch_behind_quantizer(false);
     if (r != kOk) return r;
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;
+    const BehindQuantizer dependent;
     return dense_gemm_dequant(w.hq, Wd, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
                               force_dense_bn());
 }
@@ -269,11 +275,14 @@ int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint
     const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
     int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
     if (r != kOk) return r;
+    pair_launch_behind_quantizer(true);
     r = sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, w.xq, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h,
                           M, d_model, d_ffn, S(stream), force_sparse_bt());
+    pair_launch_behind_quantizer(false);
     if (r != kOk) return r;
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;
+    const BehindQuantizer dependent;
     return sparse_gemm_dequant(Wd_comp, w.hq, wd_meta, w.hs, H(wd_scale), H(bd), H(out), M, d_ffn, d_model, S(stream),
                                force_sparse_bt());
 }

@@ -242,6 +242,10 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     cluster_sync_all();   // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *bars.tmem_slot;
+    // When the launch is a programmatic dependent of the quantizer that produces this GEMM's
+    // activations (pair_launch_behind_quantizer), everything above ran under that kernel's tail;
+    // nothing below touches global memory before this returns. In an ordinary launch it is a no-op.
+    griddep_wait();
 
     // Two TMA producers per CTA: warp 0 loads the A slab and arms the stage's barrier with the byte
     // count of the whole stage (both CTAs), the last warp loads the B slab.
@@ -575,6 +579,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *bars.tmem_slot;
     const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
+    griddep_wait();   // see dense_pair_kernel
 
     // Two TMA producers per CTA. One iteration of a producer (wait for the free stage, arm, issue) costs
     // the issuing thread about 310 clocks plus 60-100 per additional load, whatever the box size
@@ -974,6 +979,9 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 // ============================================================================================
 // Host side.
 
+// Set by pair_launch_behind_quantizer for the calling thread's next pair launch.
+thread_local bool g_behind_quantizer = false;
+
 // Launches `kern` as clusters of two CTAs; grid = 2 x min(tiles, co-resident clusters).
 // Returns kOk, kLaunchFailed, or -1 when no cluster of this kernel fits (caller falls back to the
 // single-CTA kernel).
@@ -983,16 +991,20 @@ int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaSt
     int dev = 0;
     cudaGetDevice(&dev);
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream = stream;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    const int dep_knob = tuning_knob(kKnobDependentLaunch);   // 0: as requested, 1: always, 2: never
+    cfg.numAttrs = (dep_knob == 1 || (dep_knob == 0 && g_behind_quantizer)) ? 2 : 1;
+    g_behind_quantizer = false;
     int& max_pairs = max_pairs_cache[dev & 63];
     if (max_pairs == 0) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
@@ -1199,6 +1211,8 @@ int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream) {
     return launch_dense_pair<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
 }
+
+void pair_launch_behind_quantizer(bool on) { g_behind_quantizer = on; }
 
 int dense_pair_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
                      const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,

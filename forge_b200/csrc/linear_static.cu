@@ -22,6 +22,7 @@
 #include "../../include/forge_b200.h"
 #include "common.cuh"
 #include "gemm_dense.cuh"
+#include "gemm_pair.cuh"
 #include "kernels.cuh"
 
 namespace {
@@ -61,6 +62,7 @@ extern "C" int forge_int8_linear_static(const void* x, const int8_t* w_int8, con
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int r = quantize_activation(static_cast<const __half*>(x), act_int8, act_scale, M, K, s);
     if (r != kOk) return r;
+    const BehindQuantizer dependent;
     return dense_gemm_dequant(act_int8, w_int8, act_scale, static_cast<const __half*>(w_scale),
                               static_cast<const __half*>(bias), static_cast<__half*>(output), M, K, N, s,
                               tuning_knob(kKnobDenseTile));

@@ -302,6 +302,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// Programmatic dependent launch. wait: blocks until the kernel this one was launched behind (with the
+// programmatic-serialization attribute) has completed and its writes are visible; returns at once in
+// an ordinary launch. launch_dependents: this CTA no longer holds back the start of a dependent kernel.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Arrive on a barrier of another CTA of the cluster, ordering only this CTA's own earlier accesses
 // (CTA scope): enough when what the waiter consumes is tensor memory released by tcgen05 fences,
 // and it does not make the warp wait for its global stores to be acknowledged.

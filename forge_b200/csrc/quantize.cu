@@ -14,6 +14,7 @@
 // so that K up to 65536 takes the single-read path.
 #include "common.cuh"
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 // --------------------------------------------------------------------------------------------
 // Kernels that are public declarations in the reference headers keep their name, namespace,
@@ -78,6 +79,8 @@ quantize_rows_kernel(const __half* __restrict__ input, int8_t* __restrict__ outp
                      int M, int K) {
     constexpr int ROWS = BLOCK / TPR;
     constexpr int WPR = TPR / 32;   // warps per row
+    // a GEMM launched behind this kernel as a programmatic dependent may start its set-up now
+    ptx::griddep_launch_dependents();
     const int sub = threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
     const long long row = (long long)blockIdx.x * ROWS + sub;
