@@ -253,10 +253,10 @@ int forge_w8a8_gated_mlp(const void* x, const int8_t* Wg, const int8_t* Wu, cons
     const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
     int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
     if (r != kOk) return r;
-    pair_launch_behind_quantizer(true);
+    launch_behind_quantizer(true);
     r = dense_gemm_gated(w.xq, Wg, Wu, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h, M, d_model, d_ffn,
                          S(stream));
-    pair_launch_behind_quantizer(false);
+    launch_behind_quantizer(false);
     if (r != kOk) return r;
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;
@@ -275,10 +275,10 @@ int forge_sparse_w8a8_gated_mlp(const void* x, const int8_t* Wg_comp, const uint
     const MlpWorkspace w = carve_mlp_workspace(workspace, M, d_model, d_ffn);
     int r = quantize_activation(H(x), w.xq, w.xs, M, d_model, S(stream));
     if (r != kOk) return r;
-    pair_launch_behind_quantizer(true);
+    launch_behind_quantizer(true);
     r = sparse_gemm_gated(Wg_comp, wg_meta, Wu_comp, wu_meta, w.xq, w.xs, H(wg_scale), H(wu_scale), H(bg), H(bu), w.h,
                           M, d_model, d_ffn, S(stream), force_sparse_bt());
-    pair_launch_behind_quantizer(false);
+    launch_behind_quantizer(false);
     if (r != kOk) return r;
     r = quantize_activation(w.h, w.hq, w.hs, M, d_ffn, S(stream));
     if (r != kOk) return r;

@@ -138,6 +138,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // launched behind the quantizer of the same linear call (launch_behind_quantizer): the
+            // set-up above ran under that kernel's tail; A is its output
+            griddep_wait();
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
                 for (int kb = 0; kb < num_kb; kb++) {
@@ -214,6 +217,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool has_bias = (bias != nullptr);
         int local = 0;
         int sbuf = 0;
+        griddep_wait();   // the token scales are that kernel's output too
         // After a failed wait this warp keeps walking its tiles without touching TMEM, so it
         // still meets the other epilogue warps at every named barrier.
         bool ok = true;
@@ -418,9 +422,10 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
     const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const long long tiles = (long long)m_blocks * n_blocks;
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, tm_b2, tm_c, act_scale, w_scale, bias, w_scale2,
-                                                      bias2, M, N, K, status);
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    return launch_gemm(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tm_a, tm_b, tm_b2, tm_c, act_scale,
+                       w_scale, bias, w_scale2, bias2, M, N, K, status) == cudaSuccess
+               ? kOk
+               : kLaunchFailed;
 }
 
 template <int EPI>

@@ -44,4 +44,33 @@ enum TuningKnob : int {
 int tuning_knob(int key);
 void set_tuning_knob(int key, int value);
 
+// Quantize -> GEMM chains. launch_behind_quantizer(true): the calling thread's next GEMM launch directly
+// follows, on the same stream, the per-token quantizer whose output it reads, and may be launched as
+// that kernel's programmatic dependent: it starts while the quantizer drains, streams its weights at
+// once and executes griddepcontrol.wait before its first access to the activations and their scales.
+// The request is consumed by the launch (take_behind_quantizer); false withdraws it. Knob 8 overrides.
+void launch_behind_quantizer(bool on);
+bool take_behind_quantizer();
+struct BehindQuantizer {
+    BehindQuantizer() { launch_behind_quantizer(true); }
+    ~BehindQuantizer() { launch_behind_quantizer(false); }
+};
+
+// kern<<<grid, block, smem, stream>>>(args...), with the programmatic-serialization attribute when the
+// calling thread asked for it.
+template <typename Kern, typename... Args>
+inline cudaError_t launch_gemm(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = take_behind_quantizer() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 }  // namespace fb200

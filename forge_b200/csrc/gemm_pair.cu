@@ -243,9 +243,10 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *bars.tmem_slot;
     // When the launch is a programmatic dependent of the quantizer that produces this GEMM's
-    // activations (pair_launch_behind_quantizer), everything above ran under that kernel's tail;
-    // nothing below touches global memory before this returns. In an ordinary launch it is a no-op.
-    griddep_wait();
+    // activations (launch_behind_quantizer), everything above ran under that kernel's tail. The
+    // threads that read that kernel's output - the producer of the A slabs and the epilogue warps
+    // (token scales) - execute griddepcontrol.wait first; the weight slabs stream at once. In an
+    // ordinary launch the wait returns immediately.
 
     // Two TMA producers per CTA: warp 0 loads the A slab and arms the stage's barrier with the byte
     // count of the whole stage (both CTAs), the last warp loads the B slab.
@@ -258,6 +259,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             uint32_t phase = 0;
             bool ok = true;
             int it = 0;
+            if (!second) griddep_wait();   // A is the preceding quantizer's output; B (weights) is not
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const DenseItem item = dense_item(t, work);
                 const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, band);
@@ -364,6 +366,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         int local = 0;
         int sbuf = 0;
         bool ok = true;
+        griddep_wait();   // the token scales are the preceding quantizer's output
         for (int t = pair_id; t < num_tiles; t += num_pairs, local++) {
             const DenseItem item = dense_item(t, work);
             const TileCoord tc = tile_coord(item.tile, m_blocks, n_blocks, band);
@@ -579,7 +582,6 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *bars.tmem_slot;
     const uint32_t tmem_meta = tmem_base + Cfg::kAccCols;
-    griddep_wait();   // see dense_pair_kernel
 
     // Two TMA producers per CTA. One iteration of a producer (wait for the free stage, arm, issue) costs
     // the issuing thread about 310 clocks plus 60-100 per additional load, whatever the box size
@@ -597,6 +599,8 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             int it = 0;
+            // as in dense_pair_kernel: only the activation producer waits for the preceding quantizer
+            if (producer == 1) griddep_wait();
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 const TileCoord tc = tile_coord(t, w_blocks, t_blocks, kSparseBand);
                 const int w_row = tc.a_blk * 2 * CTA_W + (int)rank * CTA_W;
@@ -757,6 +761,7 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int chunk0 = (warp_id - 2) >> 2;
         const bool has_bias = (bias != nullptr);
         int local = 0;
+        griddep_wait();   // the token scales are the preceding quantizer's output
         if (EPI == 2) {
             const bool is_gate = q < 2;
             const int pair = (q & 1) + 2 * chunk0;   // 0 .. kSpEpiWarps/2 - 1
@@ -979,9 +984,6 @@ sparse_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 // ============================================================================================
 // Host side.
 
-// Set by pair_launch_behind_quantizer for the calling thread's next pair launch.
-thread_local bool g_behind_quantizer = false;
-
 // Launches `kern` as clusters of two CTAs; grid = 2 x min(tiles, co-resident clusters).
 // Returns kOk, kLaunchFailed, or -1 when no cluster of this kernel fits (caller falls back to the
 // single-CTA kernel).
@@ -1002,9 +1004,7 @@ int launch_pairs(Kern kern, int threads, int smem_bytes, long long tiles, cudaSt
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream = stream;
     cfg.attrs = attr;
-    const int dep_knob = tuning_knob(kKnobDependentLaunch);   // 0: as requested, 1: always, 2: never
-    cfg.numAttrs = (dep_knob == 1 || (dep_knob == 0 && g_behind_quantizer)) ? 2 : 1;
-    g_behind_quantizer = false;
+    cfg.numAttrs = take_behind_quantizer() ? 2 : 1;
     int& max_pairs = max_pairs_cache[dev & 63];
     if (max_pairs == 0) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
@@ -1211,8 +1211,6 @@ int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream) {
     return launch_dense_pair<1>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
 }
-
-void pair_launch_behind_quantizer(bool on) { g_behind_quantizer = on; }
 
 int dense_pair_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
                      const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,

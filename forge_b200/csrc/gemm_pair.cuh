@@ -12,17 +12,6 @@ int dense_pair_s32(const int8_t* A, const int8_t* B, int32_t* out, int M, int K,
 int dense_pair_dequant(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale,
                        const __half* bias, __half* out, int M, int K, int N, cudaStream_t stream);
 
-// on: the calling thread's next CTA-pair launch directly follows, on the same stream, the per-token
-// quantizer whose output it reads, and is launched as that kernel's programmatic dependent: its
-// set-up (barriers, tensor memory, descriptor fetch) overlaps the quantizer's tail and it waits
-// (griddepcontrol.wait) before its first access to global memory. Measured on the 4096^3 W8A8
-// linear call: 66.6 -> 63.5 us. The request is consumed by the launch; off withdraws it.
-void pair_launch_behind_quantizer(bool on);
-struct BehindQuantizer {
-    BehindQuantizer() { pair_launch_behind_quantizer(true); }
-    ~BehindQuantizer() { pair_launch_behind_quantizer(false); }
-};
-
 // out[m][n] = SiLU(gate) * up of the two dequantised products, N output columns (256 x 128 per pair tile).
 int dense_pair_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
                      const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,

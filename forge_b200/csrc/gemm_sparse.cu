@@ -155,21 +155,25 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
     if (warp_id == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // Iterations are numbered over this CTA's (tile, K slab) sequence. A stage's loads come in two
+        // parts - weights + metadata, then the two activation atoms - because the weights are static
+        // while the activations may be the output of a quantizer this kernel was launched behind
+        // (launch_behind_quantizer): the first ring fill requests all its weight slabs at once, then
+        // waits for that kernel (griddepcontrol.wait; immediate in an ordinary launch), then requests
+        // the activations. With few tokens the call is a pass over the weights, which so starts
+        // under the quantizer's tail.
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int total = my_tiles * num_kb;
+            auto issue = [&](int it, bool weights, bool acts) {
+                const int stage = it % Cfg::kStages;
+                const int t = blockIdx.x + (it / num_kb) * gridDim.x;
+                const int kb = it % num_kb;
                 const TileCoord tc = tile_coord(t, w_blocks, t_blocks);
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-                        atomicExch(status, 201);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
-                    uint8_t* sb = sa + Cfg::kABytes;
-                    uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
+                uint8_t* sa = smem_stage + stage * Cfg::kStageBytes;
+                uint8_t* sb = sa + Cfg::kABytes;
+                uint8_t* sm = sb + 2 * Cfg::kBAtomBytes;
+                if (weights) {
                     mbar_expect_tx(&meta_full[stage], kMetaBytes);
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes - kMetaBytes);
                     if (EPI == 2) {
@@ -186,13 +190,24 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                         tma_load_3d(sm, &tm_meta, &meta_full[stage], 0, tc.w_blk * BW, kb * 2);
                         tma_load_2d(sa, &tm_w, &full_bar[stage], kb * (SLAB_K / 2), tc.w_blk * BW);
                     }
+                }
+                if (acts) {
                     tma_load_2d(sb, &tm_x, &full_bar[stage], kb * SLAB_K, tc.t_blk * BT);
                     tma_load_2d(sb + Cfg::kBAtomBytes, &tm_x, &full_bar[stage], kb * SLAB_K + 128, tc.t_blk * BT);
-                    if (++stage == Cfg::kStages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
                 }
+            };
+            const int pre = min(Cfg::kStages, total);   // the ring starts empty: no wait for these stages
+            for (int it = 0; it < pre; it++) issue(it, true, false);
+            griddep_wait();
+            for (int it = 0; it < pre; it++) issue(it, false, true);
+            for (int it = pre; it < total; it++) {
+                const int stage = it % Cfg::kStages;
+                const uint32_t phase = (uint32_t)(it / Cfg::kStages) & 1u;
+                if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+                    atomicExch(status, 201);
+                    break;
+                }
+                issue(it, true, true);
             }
         }
     } else if (warp_id == 1) {
@@ -277,6 +292,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int chunk0 = (warp_id - 2) >> 2;     // 0 or 1: which alternate chunks this warp takes
         const bool has_bias = (bias != nullptr);
         int local = 0;
+        griddep_wait();   // the token scales may be the output of the quantizer this kernel was launched behind
         if (EPI == 2) {
             // lanes 0-63 hold gate rows, lanes 64-127 the up rows of the same output columns
             const bool is_gate = q < 2;
@@ -455,9 +471,10 @@ int launch_sparse(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta,
     const int grid = (int)std::min<long long>(tiles, sm_count());
     OutDst md = {};
     if (multi != nullptr) md = *multi;
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm_w, tm_x, tm_meta, tm_w2, tm_meta2, out, md, act_scale,
-                                                      w_scale, bias, w_scale2, bias2, M, N_out, K, status);
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    return launch_gemm(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tm_w, tm_x, tm_meta, tm_w2, tm_meta2, out,
+                       md, act_scale, w_scale, bias, w_scale2, bias2, M, N_out, K, status) == cudaSuccess
+               ? kOk
+               : kLaunchFailed;
 }
 
 template <int EPI>

@@ -21,6 +21,7 @@
 // bit-identical to them. Replaces, for M <= 2, the reference's split-K small-M configurations
 // (src/gemm/int8_sparse.cu:610-632, 885-920).
 #include "common.cuh"
+#include "ptx.cuh"
 #include "gemm_dense.cuh"
 #include "gemm_sparse.cuh"
 
@@ -147,6 +148,9 @@ sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restri
     load_row(row0, wv, mv);   // in flight while the activations are fetched
     RowScale rs = load_row_scale<EPI>(w_scale, bias, row0), rs_next = rs;
     const bool has_bias = bias != nullptr;
+    // launched behind the quantizer of the same linear call: the first weight row is already in
+    // flight; the activations and their scales are that kernel's output
+    ptx::griddep_wait();
     float as[MT];
 #pragma unroll
     for (int m = 0; m < MT; m++) as[m] = (EPI == 1 && m < M) ? act_scale[m] : 0.f;
@@ -225,6 +229,7 @@ sparse_gemv_smem_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restr
         load_head(row0, wv, mv);   // in flight while the activations are staged
         rs = load_row_scale<EPI>(w_scale, bias, row0);
     }
+    ptx::griddep_wait();   // see sparse_gemv_reg_kernel
     for (int i = threadIdx.x; i < MT * chunks * 2; i += kGemvThreads) {
         const int m = i / (chunks * 2);
         const int r = i - m * chunks * 2;
@@ -296,9 +301,10 @@ int launch_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, c
         // resident CTAs per SM by register use; every warp has two rows of weights in flight
         const int per_sm = MT <= 2 ? 2 : 1;
         const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * per_sm);
-        sparse_gemv_reg_kernel<MT, EPI><<<grid, kGemvThreads, 0, stream>>>(W_comp, x, w_meta, act_scale, w_scale, bias,
-                                                                         out, M, K, N_out);
-        return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+        return launch_gemm(sparse_gemv_reg_kernel<MT, EPI>, dim3(grid), dim3(kGemvThreads), 0, stream, W_comp, x, w_meta,
+                           act_scale, w_scale, bias, out, M, K, N_out) == cudaSuccess
+                   ? kOk
+                   : kLaunchFailed;
     }
     const size_t smem = (size_t)MT * K;   // MT token rows of K bytes
     auto kern = sparse_gemv_smem_kernel<MT, EPI>;
@@ -312,8 +318,10 @@ int launch_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, c
     }
     const int per_sm = smem <= 16 * 1024 ? (MT == 1 ? 4 : 3) : (smem <= 48 * 1024 ? 2 : 1);
     const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * per_sm);
-    kern<<<grid, kGemvThreads, smem, stream>>>(W_comp, x, w_meta, act_scale, w_scale, bias, out, M, K, N_out);
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    return launch_gemm(kern, dim3(grid), dim3(kGemvThreads), smem, stream, W_comp, x, w_meta, act_scale, w_scale, bias, out,
+                       M, K, N_out) == cudaSuccess
+               ? kOk
+               : kLaunchFailed;
 }
 
 }  // namespace

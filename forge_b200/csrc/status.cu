@@ -59,6 +59,17 @@ void set_tuning_knob(int key, int value) {
     if (key >= 0 && key < kNumKnobs) g_knobs[key].store(value, std::memory_order_relaxed);
 }
 
+namespace {
+thread_local bool g_behind_quantizer = false;
+}
+void launch_behind_quantizer(bool on) { g_behind_quantizer = on; }
+bool take_behind_quantizer() {
+    const int knob = tuning_knob(kKnobDependentLaunch);   // 0: as requested, 1: always, 2: never
+    const bool take = knob == 1 || (knob == 0 && g_behind_quantizer);
+    g_behind_quantizer = false;
+    return take;
+}
+
 int tuning_knob(int key) { return (key >= 0 && key < kNumKnobs) ? g_knobs[key].load(std::memory_order_relaxed) : 0; }
 
 }  // namespace fb200
