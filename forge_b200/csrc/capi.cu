@@ -145,6 +145,8 @@ int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uin
 // against 17 us). Hence: fuse when the kernel can take K, the activation does not fit L2, and the
 // layer is narrow.
 int forge_sparse_int8_linear_fused(int M, int K, int N_out) {
+    // one and two tokens: the weight-streaming kernel quantizes the token rows itself (sparse_gemv_fq)
+    if (M >= 1 && M <= 2 && N_out > 0 && K > 0 && K % 32 == 0 && K <= 4096) return 1;
     if (M <= 0 || N_out <= 0 || K <= 0 || K % 128 != 0 || K > 1280) return 0;
     if ((size_t)M * K * 2 <= l2_bytes()) return 0;
     return (N_out <= 640 || (N_out <= 1280 && K <= 1024)) ? 1 : 0;
@@ -157,6 +159,9 @@ int forge_sparse_int8_linear(const void* x, const int8_t* W_comp, const uint32_t
     if (M <= 0 || K <= 0 || N_out <= 0) return kOk;
     // Fused quantize + GEMM: forced, or chosen when the caller did not ask for a specific split-K
     // (same rule as the reference, int8_sparse.cu:1026-1034). It does not touch the scratch buffers.
+    if (path != FORGE_SPARSE_LINEAR_TWO_PASS && split_k <= 1 && sparse_gemv_fq_fits(M, K, x) && aligned16(W_comp) &&
+        (reinterpret_cast<uintptr_t>(w_meta) & 3) == 0)
+        return sparse_gemv_fq(W_comp, H(x), w_meta, H(w_scale), H(bias), H(output), M, K, N_out, S(stream));
     const bool can_fuse = sparse_fq_fits(K, x) && aligned16(W_comp) && aligned16(w_meta);
     if (can_fuse && (path == FORGE_SPARSE_LINEAR_FUSED ||
                      (path == FORGE_SPARSE_LINEAR_AUTO && split_k <= 1 &&

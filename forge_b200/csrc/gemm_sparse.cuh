@@ -26,6 +26,12 @@ int sparse_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, c
                 const __half* w_scale, const __half* bias, void* out, int M, int K, int N_out, cudaStream_t stream,
                 int epi);
 
+// One or two tokens of FP16 activations: per-token quantization inside the streaming kernel (same bits as
+// quantize + sparse GEMM, no scratch). fits: M <= 2, K <= 4096, K % 32 == 0, x 16-byte aligned, no pinned tile.
+bool sparse_gemv_fq_fits(int M, int K, const void* x);
+int sparse_gemv_fq(const int8_t* W_comp, const __half* x, const uint32_t* w_meta, const __half* w_scale,
+                   const __half* bias, __half* out, int M, int K, int N_out, cudaStream_t stream);
+
 // out (M,N_out) s32 = x (M,K) s8 x W24 (N_out,K)^T, W24 given as W_comp (N_out,K/2) + w_meta (N_out,K/32).
 // force_bt: 32/64/128 pins the token-tile width, anything else selects it automatically.
 int sparse_gemm_s32(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, int32_t* out, int M, int K,

@@ -119,9 +119,13 @@ __device__ __forceinline__ void gemv_store(int (&acc)[MT], int lane, int row, vo
 // every weight row, so it lives in registers for the whole kernel - no shared memory, no barrier.
 // The next row's weights are requested before the current row is reduced.
 // EPI 0: out is int32 (M, N_out); EPI 1: fp16 dequant (+ bias).
-template <int MT, int EPI>
+// FQ: `x` holds the FP16 activations instead (M rows of K halves) and `act_scale` is unused: every
+// warp quantizes the token rows itself - it holds a whole row across its lanes, so the row maximum
+// is a warp reduction - with the quantizer's exact arithmetic (quantize_rows_kernel), which makes
+// the call bit-identical to quantize + GEMM without the second launch and the int8 round trip.
+template <int MT, int EPI, bool FQ = false>
 __global__ void __launch_bounds__(kGemvThreads)
-sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restrict__ x,
+sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const void* __restrict__ x_any,
                        const uint32_t* __restrict__ w_meta, const float* __restrict__ act_scale,
                        const __half* __restrict__ w_scale, const __half* __restrict__ bias, void* __restrict__ out,
                        int M, int K, int N_out) {
@@ -129,7 +133,7 @@ sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restri
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * kGemvWarps + warp;
     const int row_step = gridDim.x * kGemvWarps;
-    if (row0 >= N_out) return;
+    if (!FQ && row0 >= N_out) return;   // FQ: every warp takes part in the block-wide quantization first
 
     uint4 wv[4], wn[4];
     uint32_t mv[4], mn[4];
@@ -145,28 +149,100 @@ sparse_gemv_reg_kernel(const int8_t* __restrict__ W_comp, const int8_t* __restri
             }
         }
     };
-    load_row(row0, wv, mv);   // in flight while the activations are fetched
-    RowScale rs = load_row_scale<EPI>(w_scale, bias, row0), rs_next = rs;
+    RowScale rs = {0.f, 0.f}, rs_next = rs;
+    if (row0 < N_out) {
+        load_row(row0, wv, mv);   // in flight while the activations are fetched
+        rs = load_row_scale<EPI>(w_scale, bias, row0);
+        rs_next = rs;
+    }
     const bool has_bias = bias != nullptr;
     // launched behind the quantizer of the same linear call: the first weight row is already in
     // flight; the activations and their scales are that kernel's output
     ptx::griddep_wait();
     float as[MT];
-#pragma unroll
-    for (int m = 0; m < MT; m++) as[m] = (EPI == 1 && m < M) ? act_scale[m] : 0.f;
-
     uint4 xa[4][MT], xb[4][MT];
+    if constexpr (!FQ) {
+        const int8_t* x = static_cast<const int8_t*>(x_any);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int c = i * 32 + lane;
+        for (int m = 0; m < MT; m++) as[m] = (EPI == 1 && m < M) ? act_scale[m] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = i * 32 + lane;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                xa[i][m] = make_uint4(0, 0, 0, 0);
+                xb[i][m] = make_uint4(0, 0, 0, 0);
+                if (c < chunks && m < M) {
+                    const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * 32);
+                    xa[i][m] = p[0];
+                    xb[i][m] = p[1];
+                }
+            }
+        }
+    } else {
+        // The block quantizes each token row once into shared memory: thread t holds 16-byte pieces t and
+        // t + 256 of the row (K <= 4096: at most 512 pieces), the row maximum is a warp reduction plus one
+        // exchange through shared memory, and every lane then picks up its chunks as int8.
+        const __half* xh = static_cast<const __half*>(x_any);
+        __shared__ __align__(16) uint8_t xq_s[MT][4096];
+        __shared__ float part[MT][kGemvWarps];
+        const int nvec = K >> 3;
+        uint4 hv[MT][2];
+        float scale_m[MT], inv_m[MT];
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            xa[i][m] = make_uint4(0, 0, 0, 0);
-            xb[i][m] = make_uint4(0, 0, 0, 0);
-            if (c < chunks && m < M) {
-                const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * 32);
-                xa[i][m] = p[0];
-                xb[i][m] = p[1];
+            __half2 hmax = __float2half2_rn(0.f);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int idx = threadIdx.x + u * kGemvThreads;
+                hv[m][u] = make_uint4(0u, 0u, 0u, 0u);
+                if (m < M && idx < nvec) hv[m][u] = __ldg(reinterpret_cast<const uint4*>(xh + (size_t)m * K) + idx);
+                const __half2* h = reinterpret_cast<const __half2*>(&hv[m][u]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) hmax = __hmax2(hmax, __habs2(h[e]));
+            }
+            float tmax = max_ftz(__low2float(hmax), __high2float(hmax));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) tmax = max_ftz(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+            if (lane == 0) part[m][warp] = tmax;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            float r = part[m][0];
+#pragma unroll
+            for (int w = 1; w < kGemvWarps; w++) r = max_ftz(r, part[m][w]);
+            quant_scale(r, scale_m[m], inv_m[m]);
+            as[m] = (m < M) ? scale_m[m] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int idx = threadIdx.x + u * kGemvThreads;
+                if (idx < nvec) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&hv[m][u]);
+                    int q[8];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(h[e]);
+                        q[2 * e] = cvt_rni_ftz(mul_ftz(f.x, inv_m[m]));
+                        q[2 * e + 1] = cvt_rni_ftz(mul_ftz(f.y, inv_m[m]));
+                    }
+                    *reinterpret_cast<uint2*>(&xq_s[m][idx * 8]) =
+                        make_uint2(pack4_sat(q[0], q[1], q[2], q[3]), pack4_sat(q[4], q[5], q[6], q[7]));
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = i * 32 + lane;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                xa[i][m] = make_uint4(0, 0, 0, 0);
+                xb[i][m] = make_uint4(0, 0, 0, 0);
+                if (c < chunks && m < M) {
+                    xa[i][m] = *reinterpret_cast<const uint4*>(&xq_s[m][c * 32]);
+                    xb[i][m] = *reinterpret_cast<const uint4*>(&xq_s[m][c * 32 + 16]);
+                }
             }
         }
     }
@@ -301,8 +377,8 @@ int launch_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, c
         // resident CTAs per SM by register use; every warp has two rows of weights in flight
         const int per_sm = MT <= 2 ? 2 : 1;
         const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * per_sm);
-        return launch_gemm(sparse_gemv_reg_kernel<MT, EPI>, dim3(grid), dim3(kGemvThreads), 0, stream, W_comp, x, w_meta,
-                           act_scale, w_scale, bias, out, M, K, N_out) == cudaSuccess
+        return launch_gemm(sparse_gemv_reg_kernel<MT, EPI>, dim3(grid), dim3(kGemvThreads), 0, stream, W_comp,
+                           static_cast<const void*>(x), w_meta, act_scale, w_scale, bias, out, M, K, N_out) == cudaSuccess
                    ? kOk
                    : kLaunchFailed;
     }
@@ -345,6 +421,32 @@ int sparse_gemv(const int8_t* W_comp, const int8_t* x, const uint32_t* w_meta, c
     if (mt == 2) { FB200_GEMV(2); }
     FB200_GEMV(4);
 #undef FB200_GEMV
+}
+
+// FP16 activations in, FP16 result out: the per-token quantization happens inside the streaming kernel
+// (one or two tokens, K <= 4096, K % 32 == 0, x 16-byte aligned). Same bits as quantize + sparse GEMM.
+bool sparse_gemv_fq_fits(int M, int K, const void* x) {
+    return M >= 1 && M <= 2 && K % 32 == 0 && K <= 4096 && aligned16(x) && tuning_knob(kKnobGemvVariant) != 2 &&
+           tuning_knob(kKnobSparseTile) == 0;
+}
+
+int sparse_gemv_fq(const int8_t* W_comp, const __half* x, const uint32_t* w_meta, const __half* w_scale,
+                   const __half* bias, __half* out, int M, int K, int N_out, cudaStream_t stream) {
+    if (W_comp == nullptr || x == nullptr || w_meta == nullptr || w_scale == nullptr || out == nullptr)
+        return kBadPointer;
+    if (!device_is_sm100()) return kUnsupportedArch;
+    const long long blocks_for_rows = ((long long)N_out + kGemvWarps - 1) / kGemvWarps;
+    const int grid = (int)std::min<long long>(blocks_for_rows, (long long)sm_count() * 2);
+    cudaError_t e;
+    if (M == 1)
+        e = launch_gemm(sparse_gemv_reg_kernel<1, 1, true>, dim3(grid), dim3(kGemvThreads), 0, stream, W_comp,
+                        static_cast<const void*>(x), w_meta, static_cast<const float*>(nullptr), w_scale, bias,
+                        static_cast<void*>(out), M, K, N_out);
+    else
+        e = launch_gemm(sparse_gemv_reg_kernel<2, 1, true>, dim3(grid), dim3(kGemvThreads), 0, stream, W_comp,
+                        static_cast<const void*>(x), w_meta, static_cast<const float*>(nullptr), w_scale, bias,
+                        static_cast<void*>(out), M, K, N_out);
+    return e == cudaSuccess ? kOk : kLaunchFailed;
 }
 
 }  // namespace fb200

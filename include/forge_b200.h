@@ -131,7 +131,10 @@ int forge_sparse_int8_gemm(const int8_t* W_comp, const int8_t* x_int8, const uin
                            const float* act_scale, const void* w_scale, const void* bias, void* output, int M, int K,
                            int N_out, float* splitk_workspace, int split_k, forge_stream_t stream, int tile);
 
-/* forge::gemm::sparse_int8_linear_fused - include/forge/gemm/int8_sparse.cuh:78-83. 1 or 0. */
+/* forge::gemm::sparse_int8_linear_fused - include/forge/gemm/int8_sparse.cuh:78-83. 1 or 0: whether the
+ * automatic path of forge_sparse_int8_linear quantizes inside the GEMM kernel - the tcgen05 kernel for
+ * narrow layers with K <= 1280 whose activation does not fit L2, the weight-streaming kernel for one and
+ * two tokens with K <= 4096. Neither touches the scratch buffers. */
 int forge_sparse_int8_linear_fused(int M, int K, int N_out);
 
 /* forge::gemm::sparse_int8_linear - include/forge/gemm/int8_sparse.cuh:90-105,

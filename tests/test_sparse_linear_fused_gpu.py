@@ -114,3 +114,30 @@ def test_auto_path_takes_the_fused_kernel_where_the_policy_says_so():
     assert C.device_status() == 0
     assert torch.equal(out.view(torch.int16), two.view(torch.int16))
     assert int(sq.min()) == 0x5A and int(sq.max()) == 0x5A and float(ss.min()) == -7.0   # scratch untouched
+
+
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("K,N", [(4096, 11008), (1024, 300), (96, 17), (4096, 1000), (2048, 8)])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_one_and_two_tokens_quantize_inside_the_streaming_kernel(M, K, N, with_bias):
+    """One- and two-token calls (K <= 4096) take the weight-streaming kernel with the quantizer inside it:
+    no scratch is touched or needed, and the bytes are those of quantize + GEMM. Inputs include a zero row
+    element pattern and large magnitudes."""
+    lib = _lib.load()
+    assert lib.forge_sparse_int8_linear_fused(M, K, N) == 1
+    W, x, w_s, bias, comp, meta = _prep(M, K, N, 4000 + M + K + N)
+    x[0, :7] = torch.tensor([0.0, -0.0, 65504.0, -65504.0, 6e-8, 1.5, -2.5], dtype=torch.float16)
+    dx, dws = x.to(DEV), w_s.to(DEV)
+    dbias = bias.to(DEV) if with_bias else None
+    two, _, _ = _linear(dx, comp, meta, dws, dbias, TWO_PASS)
+    for path in (AUTO, FUSED):
+        got, _, _ = _linear(dx, comp, meta, dws, dbias, path, with_scratch=False)
+        assert torch.equal(got.view(torch.int16), two.view(torch.int16)), f"path {path}"
+    # non-finite activations: same bytes as the two-pass path there too
+    x2 = x.clone()
+    x2[M - 1, 3] = float("inf")
+    x2[0, 5] = float("nan")
+    d2 = x2.to(DEV)
+    two2, _, _ = _linear(d2, comp, meta, dws, dbias, TWO_PASS)
+    got2, _, _ = _linear(d2, comp, meta, dws, dbias, AUTO, with_scratch=False)
+    assert torch.equal(got2.view(torch.int16), two2.view(torch.int16))
