@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libforge_b200.so")
-SOURCES = ["capi.cu", "status.cu", "quantize.cu", "sparsity.cu", "gemm_dense.cu", "gemm_sparse.cu", "gemm_pair.cu", "gemm_fq.cu", "sparse_gemv.cu", "probes.cu", "linear_static.cu", "conv.cu"]
+SOURCES = ["capi.cu", "status.cu", "quantize.cu", "sparsity.cu", "gemm_dense.cu", "gemm_sparse.cu", "gemm_pair.cu", "gemm_fq.cu", "sparse_gemv.cu", "dense_gemv.cu", "probes.cu", "linear_static.cu", "conv.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -83,6 +83,10 @@ int forge_int8_dp4a_gemm_dequant(const int8_t* A, const int8_t* B, const float* 
 int forge_int8_linear(const void* x, const int8_t* w_int8, const void* w_scale, const void* bias, void* output,
                       int M, int K, int N, int8_t* scratch_a_int8, float* scratch_a_scale, forge_stream_t stream) {
     if (M <= 0 || K <= 0 || N <= 0) return kOk;
+    // very few tokens: the weight-streaming kernel quantizes the token rows itself (no scratch traffic)
+    if (x != nullptr && w_int8 != nullptr && w_scale != nullptr && output != nullptr && dense_gemv_fits(M, K, w_int8, x) &&
+        device_is_sm100())
+        return dense_gemv_fq(w_int8, H(x), H(w_scale), H(bias), H(output), M, K, N, S(stream));
     const int r = quantize_activation(H(x), scratch_a_int8, scratch_a_scale, M, K, S(stream));
     if (r != kOk) return r;
     const BehindQuantizer dependent;

@@ -435,6 +435,9 @@ int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, con
     if (A == nullptr || B == nullptr || out == nullptr) return kBadPointer;
     if (EPI == 1 && (act_scale == nullptr || w_scale == nullptr)) return kBadPointer;
     if (!device_is_sm100()) return kUnsupportedArch;
+    // very few tokens: one pass over the weights on the CUDA cores (dense_gemv.cu)
+    if (force_bn == 0 && dense_gemv_fits(M, K, B, A))
+        return dense_gemv(B, A, act_scale, w_scale, bias, out, M, K, N, stream, EPI);
     const int out_esz = (EPI == 0) ? 4 : 2;
     const bool tma_ok = (K % 16 == 0) && ((long long)N * out_esz % 16 == 0) && aligned16(A) && aligned16(B) &&
                         aligned16(out);

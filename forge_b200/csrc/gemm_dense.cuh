@@ -17,6 +17,14 @@ int dense_gemm_dequant(const int8_t* A, const int8_t* B, const float* act_scale,
 // out (M,N) fp16 = fp16(SiLU(g) * u), g = (act_scale*wg_scale)*acc_g + bg, u likewise from Wu: the
 // gate and up projections of a gated MLP in one GEMM pass. Wg, Wu (N,K) s8; bg / bu may be null.
 // Needs K % 16 == 0, N % 8 == 0 and 16-byte aligned A, Wg, Wu, out (else kBadShape).
+// Weight-streaming CUDA-core kernel for very few tokens (dense_gemv.cu). epi 0: out int32 (M,N); 1: fp16 dequant
+// (+ bias). dense_gemv_fq: FP16 activations, quantized inside the kernel (the bits of quantize + GEMM).
+bool dense_gemv_fits(int M, int K, const void* W, const void* x);
+int dense_gemv(const int8_t* W, const int8_t* x, const float* act_scale, const __half* w_scale, const __half* bias,
+               void* out, int M, int K, int N, cudaStream_t stream, int epi);
+int dense_gemv_fq(const int8_t* W, const __half* x, const __half* w_scale, const __half* bias, __half* out, int M, int K,
+                  int N, cudaStream_t stream);
+
 int dense_gemm_gated(const int8_t* A, const int8_t* Wg, const int8_t* Wu, const float* act_scale,
                      const __half* wg_scale, const __half* wu_scale, const __half* bg, const __half* bu, __half* out,
                      int M, int K, int N, cudaStream_t stream);
@@ -39,6 +47,7 @@ enum TuningKnob : int {
     kKnobGemvVariant = 5,      // 1-4 token sparse kernel: 1 = token slices in registers, 2 = in shared memory
     kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)
     kKnobDenseBand = 7,        // dense CTA-pair kernel: 256-row blocks per raster band
+    kKnobGemvDenseMaxTokens = 9,  // dense streaming kernel: largest M it takes (default 4, at most 16; negative: never)
     kKnobDependentLaunch = 8,  // CTA-pair kernels as programmatic dependents: 0 = where requested, 1 = always, 2 = never
 };
 int tuning_knob(int key);

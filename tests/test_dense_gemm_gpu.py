@@ -147,3 +147,77 @@ def test_int8_linear_matches_quantize_then_gemm():
                                 ref.data_ptr(), M, K, N, sa2.data_ptr(), ss2.data_ptr(), O.cur_stream())
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
+GEMV_SHAPES = [(1, 4096, 11008), (2, 4096, 1000), (3, 16, 8), (5, 4112, 300), (8, 8192, 520), (16, 4096, 2000),
+               (16, 12288, 64), (7, 14336, 96), (1, 32, 9)]
+
+
+@pytest.mark.parametrize("M,K,N", GEMV_SHAPES)
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_few_token_streaming_kernel_same_bits_as_the_tensor_core_kernel(M, K, N, with_bias):
+    """Up to 16 tokens the dense GEMM is a weight-streaming CUDA-core kernel (dense_gemv.cu). Its INT32 output
+    must equal the host loop, its FP16 output the tensor-core kernel's (pinned tile) and the reference kernel's."""
+    lib = _lib.load()
+    lib.forge_b200_set_tuning(9, 16)   # the kernel has instances up to 16 tokens; the default stops at 8
+    try:
+        _few_token_case(lib, M, K, N, with_bias)
+    finally:
+        lib.forge_b200_set_tuning(9, 0)
+
+
+def _few_token_case(lib, M, K, N, with_bias):
+    A, B, a_s, w_s, bias = _inputs(M, K, N, 500 + M + K + N)
+    dA, dB, das, dws = A.to(DEV), B.to(DEV), a_s.to(DEV), w_s.to(DEV)
+    dbias = bias.to(DEV) if with_bias else None
+    out32 = torch.full((M, N), 0x7B7B7B7B, dtype=torch.int32, device=DEV)
+    _lib.call("forge_int8_gemm_s32", dA.data_ptr(), dB.data_ptr(), out32.data_ptr(), M, K, N, 0)
+    _status_ok()
+    assert np.array_equal(out32.cpu().numpy(), O.gemm_s32(A.numpy(), B.numpy()))
+    streamed = C.int8_gemm_dequant(dA, dB, das, dws, dbias)
+    _status_ok()
+    lib.forge_b200_set_dense_tile(64)        # a pinned tile keeps the tcgen05 kernel
+    try:
+        tensor = C.int8_gemm_dequant(dA, dB, das, dws, dbias)
+        _status_ok()
+    finally:
+        lib.forge_b200_set_dense_tile(0)
+    assert torch.equal(streamed.view(torch.int16), tensor.view(torch.int16))
+    O.require_ref()
+    ref = O.ref_int8_gemm_dequant(dA, dB, das, dws, dbias)
+    assert torch.equal(streamed.view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 11008), (2, 1024, 300), (4, 4096, 1000), (16, 4096, 520), (9, 8192, 64),
+                                   (3, 48, 24)])
+def test_few_token_int8_linear_quantizes_inside_the_streaming_kernel(M, K, N):
+    """int8_linear with a few tokens: one kernel, scratch untouched, the bytes of quantize + GEMM - also with
+    non-finite activations."""
+    lib = _lib.load()
+    lib.forge_b200_set_tuning(9, 16)
+    try:
+        _few_token_linear_case(M, K, N)
+    finally:
+        lib.forge_b200_set_tuning(9, 0)
+
+
+def _few_token_linear_case(M, K, N):
+    g = torch.Generator().manual_seed(70 + M + K + N)
+    x = (torch.randn((M, K), generator=g) * 3).to(torch.float16)
+    x[0, :4] = torch.tensor([0.0, 65504.0, -65504.0, 6e-8], dtype=torch.float16)
+    _, B, _, w_s, bias = _inputs(M, K, N, 71)
+    dB, dws, dbias = B.to(DEV), w_s.to(DEV), bias.to(DEV)
+    for variant in range(2):
+        if variant == 1:
+            x[M - 1, 1] = float("inf")
+            x[0, 2] = float("nan")
+        dx = x.to(DEV)
+        sa = torch.full((M, K), 0x5A, dtype=torch.int8, device=DEV)
+        ss = torch.full((M,), -7.0, dtype=torch.float32, device=DEV)
+        out = C.int8_linear(dx, dB, dws, dbias, sa, ss)
+        _status_ok()
+        assert int(sa.min()) == 0x5A and int(sa.max()) == 0x5A and float(ss.max()) == -7.0   # scratch untouched
+        q, s = C.fused_quantize_activation(dx, M, K)
+        want = C.int8_gemm_dequant(q, dB, s, dws, dbias)
+        _status_ok()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), f"variant {variant}"
