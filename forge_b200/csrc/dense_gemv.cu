@@ -1,8 +1,8 @@
-// Dense INT8 GEMM for very few tokens (up to 4 by default): a weight-streaming kernel on the CUDA cores.
+// Dense INT8 GEMM for very few tokens (one or two by default): a weight-streaming kernel on the CUDA cores.
 //
 // With so few tokens int8_gemm_dequant / int8_linear is one pass over the weight (N x K bytes): the
-// tcgen05 kernel spends its time on 128-row token tiles that are almost empty and on two waves of
-// 64-column tiles (11008 x 4096 at one token: 28 us against 7 us of HBM time). Here every SM streams
+// tcgen05 kernel has fixed costs (tensor-map fetch, TMEM allocation, a 128-row token tile that is almost
+// empty) on top of the 7 us of HBM time of an 11008 x 4096 weight. Here every SM streams
 // weight rows with 16-byte loads, one row ahead; the token rows (M x K bytes) sit in shared memory,
 // where every warp reads them once per weight row (with dense weights that is one shared-memory byte
 // per HBM byte and token, far from the shared-memory limit), and DP4A accumulates in int32.
@@ -193,15 +193,14 @@ int dispatch_dense_gemv(const int8_t* W, const void* x, const float* act_scale, 
 
 }  // namespace
 
-// Shapes the streaming kernel takes: up to 4 tokens (every warp re-reads the token rows from shared memory
-// per weight row, so its time grows with M: 11008 x 4096, cold weights, 11.4 / 12.0 / 16.2 / 24.4 / 50 us at
-// 1 / 2 / 4 / 8 / 16 tokens against 25-28 us for the tcgen05 kernel; two weight rows per warp and read were
-// measured: better from 16 tokens only, where the tensor cores win anyway. Knob 9 moves the limit up to 16 or,
-// negative, switches the kernel off), K a multiple of 16, the token rows within 200 KB of shared memory,
-// 16-byte aligned operands; a pinned dense tile switches it off too.
+// Shapes the streaming kernel takes: one or two tokens (every warp re-reads the token rows from shared memory
+// per weight row, so its time grows with M: 11008 x 4096, cold weights, 11.4 / 12.0 / 15.3 / 16.2 / 24.4 us at
+// 1 / 2 / 3 / 4 / 8 tokens against 13.5 us for the tcgen05 kernel with 80-column tiles. Knob 9 moves the limit
+// up to 16 or, negative, switches the kernel off), K a multiple of 16, the token rows within 200 KB of shared
+// memory, 16-byte aligned operands; a pinned dense tile switches it off too.
 bool dense_gemv_fits(int M, int K, const void* W, const void* x) {
     const int knob = tuning_knob(kKnobGemvDenseMaxTokens);
-    const int max_tokens = knob > 0 ? std::min(16, knob) : (knob < 0 ? 0 : 4);
+    const int max_tokens = knob > 0 ? std::min(16, knob) : (knob < 0 ? 0 : 2);
     return M >= 1 && M <= max_tokens && K % 16 == 0 && (size_t)M * K <= 200 * 1024 && aligned16(W) && aligned16(x) &&
            tuning_knob(kKnobDenseTile) == 0;
 }

@@ -42,7 +42,7 @@ struct DenseCfg {
     static constexpr int kScaleBytes = 2 * BN * 2 * (int)sizeof(__half);   // [2 tiles in flight][w_scale, bias][BN]
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kScaleBytes + kBarBytes;
-    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);   // power of two >= 2 * BN
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory limit");
     static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns: power of two <= 512");
 };
@@ -76,7 +76,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
                   const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
                   const __half* __restrict__ bias, const __half* __restrict__ w_scale2,
-                  const __half* __restrict__ bias2, int M, int N, int K, int* __restrict__ status) {
+                  const __half* __restrict__ bias2, void* __restrict__ out, int M, int N, int K, int a_rows,
+                  int* __restrict__ status) {
+    // a_rows: rows of the A slab a TMA load fetches (128; 32 or 64 when M is that small: the other rows of
+    // the 128-row MMA operand keep whatever the buffer holds - their accumulator lanes are never stored)
     using Cfg = DenseCfg<BN>;
     extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -151,7 +154,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                     uint8_t* sa = smem_ab + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    mbar_expect_tx(&full_bar[stage], a_rows * BLOCK_K + Cfg::kBBytes);
                     tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, tc.m_blk * BLOCK_M);
                     if (EPI == 2) {
                         tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
@@ -330,6 +333,38 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 }
                 sbuf = (sbuf + 1) % Cfg::kEpiBufs;
             }
+            // Tile widths that are not a multiple of the staged chunk (BN = 80, 96, 112: chosen so that a
+            // few-token call's tiles fit one wave) end in 16-column pieces written with plain stores.
+            if constexpr (EPI != 2 && TILE_N % CH != 0) {
+#pragma unroll 1
+                for (int col = (TILE_N / CH) * CH; col < TILE_N; col += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(taddr + col, v);
+                    tmem_ld_wait();
+                    const int n = n0 + col;
+                    if (row < M && n < N) {   // N % 16 == 0 on this path: a piece is inside or outside as a whole
+                        if (EPI == 0) {
+                            int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(out) + (size_t)row * N + n);
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                dst[i] = make_int4((int)v[4 * i], (int)v[4 * i + 1], (int)v[4 * i + 2], (int)v[4 * i + 3]);
+                        } else {
+                            uint32_t h[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const float2 w = __half22float2(reinterpret_cast<const __half2*>(s_ws + col)[i]);
+                                const float2 b = __half22float2(reinterpret_cast<const __half2*>(s_bias + col)[i]);
+                                h[i] = pack_half2(
+                                    dequant_gemm(static_cast<int>(v[2 * i]), mul_ftz(as, w.x), b.x, has_bias),
+                                    dequant_gemm(static_cast<int>(v[2 * i + 1]), mul_ftz(as, w.y), b.y, has_bias));
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(out) + (size_t)row * N + n);
+                            dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                            dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                        }
+                    }
+                }
+            }
             // accumulator fully read: hand the TMEM buffer back to the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -390,11 +425,12 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
         attr_set[dev & 63] = true;
     }
     constexpr int TILE_N = (EPI == 2) ? BN / 2 : BN;
+    const int a_rows = (EPI != 2 && M <= 32) ? 32 : ((EPI != 2 && M <= 64) ? 64 : BLOCK_M);
     CUtensorMap tm_a, tm_b, tm_b2, tm_c;
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         const uint64_t str[1] = {(uint64_t)K};
-        const uint32_t box[2] = {BLOCK_K, BLOCK_M};
+        const uint32_t box[2] = {BLOCK_K, (uint32_t)a_rows};
         if (!make_tmap(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
             return kLaunchFailed;
     }
@@ -423,7 +459,7 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
     const long long tiles = (long long)m_blocks * n_blocks;
     const int grid = (int)std::min<long long>(tiles, sm_count());
     return launch_gemm(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tm_a, tm_b, tm_b2, tm_c, act_scale,
-                       w_scale, bias, w_scale2, bias2, M, N, K, status) == cudaSuccess
+                       w_scale, bias, w_scale2, bias2, out, M, N, K, a_rows, status) == cudaSuccess
                ? kOk
                : kLaunchFailed;
 }
@@ -452,7 +488,9 @@ int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, con
     // The CTA-pair kernel (256 x 256 outputs per pair of SMs; knob 512) once there are enough such
     // tiles for every SM pair: measured 7 % faster than 128 x 256 tiles at 8192^3, burst and sustained.
     const long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-    if (force_bn == 512 || (force_bn == 0 && pair_tiles >= sm_count() / 2 && K >= 512)) {
+    // (not for a single block of token rows: half of every 256-row pair tile would be empty - N = 28672, K = 8192,
+    // 64 tokens: 66.6 us against 62.5 us with 128 x 128 tiles)
+    if (force_bn == 512 || (force_bn == 0 && pair_tiles >= sm_count() / 2 && K >= 512 && M > BLOCK_M)) {
         const int r = (EPI == 0) ? dense_pair_s32(A, B, static_cast<int32_t*>(out), M, K, N, stream)
                                  : dense_pair_dequant(A, B, act_scale, w_scale, bias, static_cast<__half*>(out), M,
                                                       K, N, stream);
@@ -460,16 +498,36 @@ int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, con
     }
     // Tile width: the widest tile that still gives every SM work.
     int bn = force_bn;
-    if (bn != 64 && bn != 128 && bn != 256) {
+    if ((bn == 80 || bn == 96 || bn == 112) && N % 16 != 0) bn = 64;   // the narrow widths end in 16-column pieces
+    if (bn != 64 && bn != 80 && bn != 96 && bn != 112 && bn != 128 && bn != 256) {
         const long long m_blocks = (M + BLOCK_M - 1) / BLOCK_M;
         const int sms = sm_count();
         if (m_blocks * ((N + 255) / 256) * 5 >= sms * 3) bn = 256;   // >= 60 % of the SMs busy: wide tiles still win
         else if (m_blocks * ((N + 127) / 128) >= sms) bn = 128;
         else bn = 64;
     }
+    // One block of token rows (M <= 128): the call is a pass over the weights and its time is that of the SM with
+    // the most weight columns - 11008 columns in 64-wide tiles are 172 tiles, two waves on 148 SMs. Tile widths in
+    // steps of 16 columns: take the narrowest width whose tiles fit one wave, if that beats the default's waves x width
+    // (N = 28672, K = 8192, 64 tokens: two waves of 128 measured 6 % faster than two of 112).
+    if (force_bn == 0 && bn <= 128 && M <= BLOCK_M && N % 16 == 0) {
+        const int sms = sm_count();
+        int best = bn, best_cost = ((N + bn - 1) / bn + sms - 1) / sms * bn;
+        for (int w = 64; w <= 128; w += 16) {
+            if ((N + w - 1) / w > sms) continue;   // only widths that fit one wave (with more, the model is too coarse)
+            if (w < best_cost) {
+                best = w;
+                best_cost = w;
+            }
+        }
+        bn = best;
+    }
     switch (bn) {
     case 256: return launch_dense<256, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
     case 128: return launch_dense<128, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    case 112: return launch_dense<112, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    case 96:  return launch_dense<96, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
+    case 80:  return launch_dense<80, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
     default:  return launch_dense<64, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
     }
 }

@@ -47,7 +47,7 @@ enum TuningKnob : int {
     kKnobGemvVariant = 5,      // 1-4 token sparse kernel: 1 = token slices in registers, 2 = in shared memory
     kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)
     kKnobDenseBand = 7,        // dense CTA-pair kernel: 256-row blocks per raster band
-    kKnobGemvDenseMaxTokens = 9,  // dense streaming kernel: largest M it takes (default 4, at most 16; negative: never)
+    kKnobGemvDenseMaxTokens = 9,  // dense streaming kernel: largest M it takes (default 2, at most 16; negative: never)
     kKnobDependentLaunch = 8,  // CTA-pair kernels as programmatic dependents: 0 = where requested, 1 = always, 2 = never
 };
 int tuning_knob(int key);

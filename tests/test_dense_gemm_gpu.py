@@ -67,7 +67,7 @@ def test_dequant_bit_exact(M, K, N, with_bias):
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), "differs from the reference wmma kernel"
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 80, 96, 112, 128, 256])
 def test_every_tile_width(bn):
     M, K, N = 300, 1152, 784
     A, B, a_s, w_s, bias = _inputs(M, K, N, 5 + bn)
@@ -221,3 +221,32 @@ def _few_token_linear_case(M, K, N):
         want = C.int8_gemm_dequant(q, dB, s, dws, dbias)
         _status_ok()
         assert torch.equal(out.view(torch.int16), want.view(torch.int16)), f"variant {variant}"
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 4096, 11008), (128, 4096, 11008), (100, 1024, 28672), (37, 512, 1200),
+                                   (5, 256, 176)])
+def test_one_token_block_picks_a_width_that_fits_one_wave(M, K, N):
+    """Calls with one block of token rows choose the tile width (64 ... 128 in steps of 16) by columns per SM; the
+    narrow widths end in 16-column pieces stored by the epilogue itself. Same bits as the 64-wide tiles, the host
+    loop and the reference kernel."""
+    lib = _lib.load()
+    lib.forge_b200_set_tuning(9, -1)          # keep the tensor-core kernel for every M here
+    try:
+        A, B, a_s, w_s, bias = _inputs(M, K, N, 900 + M + K + N)
+        dA, dB, das, dws, dbias = A.to(DEV), B.to(DEV), a_s.to(DEV), w_s.to(DEV), bias.to(DEV)
+        auto16 = C.int8_gemm_dequant(dA, dB, das, dws, dbias)
+        auto32 = C.int8_gemm_s32(dA, dB)
+        _status_ok()
+        lib.forge_b200_set_dense_tile(64)
+        try:
+            fixed16 = C.int8_gemm_dequant(dA, dB, das, dws, dbias)
+            _status_ok()
+        finally:
+            lib.forge_b200_set_dense_tile(0)
+    finally:
+        lib.forge_b200_set_tuning(9, 0)
+    assert torch.equal(auto16.view(torch.int16), fixed16.view(torch.int16))
+    assert np.array_equal(auto32.cpu().numpy(), O.gemm_s32(A.numpy(), B.numpy()))
+    O.require_ref()
+    ref = O.ref_int8_gemm_dequant(dA, dB, das, dws, dbias)
+    assert torch.equal(auto16.view(torch.int16), ref.view(torch.int16))
