@@ -31,18 +31,25 @@ constexpr int kThreads = 192;
 constexpr int kEpiWarps = 4;
 constexpr int kEpiBufBytes = 32 * 128;   // one epilogue staging buffer: 32 rows x 128 bytes
 
-template <int BN>
+// KA: 128-byte K atoms per pipeline stage. 1 for the general kernel; 2 for calls with one block of token rows,
+// which are passes over the weights whose pace is set by the TMA-issuing threads (about 310 clocks per stage
+// and thread plus 80 per further load, whatever the box size): stages twice as deep and a second producer
+// thread for the weight slabs halve the issue cost per byte.
+template <int BN, int KA = 1>
 struct DenseCfg {
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
-    static constexpr int kABytes = BLOCK_M * BLOCK_K;
-    static constexpr int kBBytes = BN * BLOCK_K;
+    static constexpr int kABytes = BLOCK_M * BLOCK_K * KA;
+    static constexpr int kBBytes = BN * BLOCK_K * KA;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kEpiBufs = 2;
     static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
     static constexpr int kScaleBytes = 2 * BN * 2 * (int)sizeof(__half);   // [2 tiles in flight][w_scale, bias][BN]
     static constexpr int kBarBytes = 256;
+    static constexpr int kStagesFit = (232448 - kEpiBytes - kScaleBytes - kBarBytes) / kStageBytes;
+    static constexpr int kStages = (KA == 1) ? ((BN == 256) ? 4 : 6) : (kStagesFit > 6 ? 6 : kStagesFit);
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kScaleBytes + kBarBytes;
     static constexpr int kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);   // power of two >= 2 * BN
+    static constexpr int kThreads = (KA == 1) ? 192 : 224;   // KA 2: a seventh warp issues the B loads
+    static_assert(kStages >= 3, "pipeline depth");
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory limit");
     static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns: power of two <= 512");
 };
@@ -70,8 +77,8 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_blocks, int n_block
 //      2 = gated: the B tile is 128 rows of a gate weight followed by the same 128 rows of an up
 //          weight (tm_b / tm_b2), so accumulator columns c and 128 + c belong to output column c of
 //          the same token; the epilogue writes fp16(SiLU(g) * u) with g, u dequantised in fp32.
-template <int BN, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int EPI, int KA>
+__global__ void __launch_bounds__((DenseCfg<BN, KA>::kThreads), 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
                   const float* __restrict__ act_scale, const __half* __restrict__ w_scale,
@@ -80,7 +87,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   int* __restrict__ status) {
     // a_rows: rows of the A slab a TMA load fetches (128; 32 or 64 when M is that small: the other rows of
     // the 128-row MMA operand keep whatever the buffer holds - their accumulator lanes are never stored)
-    using Cfg = DenseCfg<BN>;
+    using Cfg = DenseCfg<BN, KA>;
     extern __shared__ __align__(1024) uint8_t smem[];
 
     uint8_t* smem_ab = smem;
@@ -106,7 +113,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     constexpr int TILE_N = (EPI == 2) ? BN / 2 : BN;   // output columns per tile
     const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const int num_tiles = m_blocks * n_blocks;
-    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int num_kb = (K + BLOCK_K * KA - 1) / (BLOCK_K * KA);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; s++) {
@@ -135,15 +142,18 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    if (warp_id == 0) {
-        // ------------------------------------------------------------------ TMA producer
+    constexpr int kBWarp = Cfg::kThreads / 32 - 1;   // KA 2: the warp that issues the B (weight) loads
+    if (warp_id == 0 || (KA == 2 && warp_id == kBWarp)) {
+        // ------------------------------------------------------------------ TMA producer(s)
+        const bool loads_a = (warp_id == 0);
+        const bool loads_b = (KA == 1) || (warp_id == kBWarp);
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             // launched behind the quantizer of the same linear call (launch_behind_quantizer): the
-            // set-up above ran under that kernel's tail; A is its output
-            griddep_wait();
+            // set-up above ran under that kernel's tail; A is its output (the weights are not)
+            if (loads_a) griddep_wait();
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
                 for (int kb = 0; kb < num_kb; kb++) {
@@ -154,13 +164,24 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                     uint8_t* sa = smem_ab + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    mbar_expect_tx(&full_bar[stage], a_rows * BLOCK_K + Cfg::kBBytes);
-                    tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, tc.m_blk * BLOCK_M);
-                    if (EPI == 2) {
-                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
-                        tma_load_2d(sb + Cfg::kBBytes / 2, &tm_b2, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
-                    } else {
-                        tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * BN);
+                    if (loads_a) {
+                        // the arming thread: bytes of every load of the stage (A atoms of a_rows rows, B atoms)
+                        mbar_expect_tx(&full_bar[stage], KA * (a_rows * BLOCK_K + BN * BLOCK_K));
+#pragma unroll
+                        for (int j = 0; j < KA; j++)
+                            tma_load_2d(sa + j * (BLOCK_M * BLOCK_K), &tm_a, &full_bar[stage], (kb * KA + j) * BLOCK_K,
+                                        tc.m_blk * BLOCK_M);
+                    }
+                    if (loads_b) {
+                        if (EPI == 2) {
+                            tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
+                            tma_load_2d(sb + Cfg::kBBytes / 2, &tm_b2, &full_bar[stage], kb * BLOCK_K, tc.n_blk * TILE_N);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < KA; j++)
+                                tma_load_2d(sb + j * (BN * BLOCK_K), &tm_b, &full_bar[stage], (kb * KA + j) * BLOCK_K,
+                                            tc.n_blk * BN);
+                        }
                     }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
@@ -195,12 +216,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_ab + stage * Cfg::kStageBytes);
-                    const uint64_t desc_a = make_desc_sw128(sa);
-                    const uint64_t desc_b = make_desc_sw128(sa + Cfg::kABytes);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                        // advancing the start address by 32 bytes (>>4 = 2) steps one UMMA_K inside the atom
-                        umma_i8(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int j = 0; j < KA; j++) {
+                        const uint64_t desc_a = make_desc_sw128(sa + j * (BLOCK_M * BLOCK_K));
+                        const uint64_t desc_b = make_desc_sw128(sa + Cfg::kABytes + j * (BN * BLOCK_K));
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                            // advancing the start address by 32 bytes (>>4 = 2) steps one UMMA_K inside the atom
+                            umma_i8(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | j | k) != 0 ? 1u : 0u);
+                        }
                     }
                     tc_commit(&empty_bar[stage]);
                     if (++stage == Cfg::kStages) {
@@ -410,15 +434,15 @@ __global__ void dense_gemm_ragged_kernel(const int8_t* __restrict__ A, const int
     }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int KA = 1>
 int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const __half* w_scale, const __half* bias,
                  void* out, int M, int K, int N, cudaStream_t stream, const int8_t* B2 = nullptr,
                  const __half* w_scale2 = nullptr, const __half* bias2 = nullptr) {
-    using Cfg = DenseCfg<BN>;
+    using Cfg = DenseCfg<BN, KA>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = dense_gemm_kernel<BN, EPI>;
+    auto kern = dense_gemm_kernel<BN, EPI, KA>;
     if (!attr_set[dev & 63]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
             return kLaunchFailed;
@@ -458,7 +482,7 @@ int launch_dense(const int8_t* A, const int8_t* B, const float* act_scale, const
     const int n_blocks = (N + TILE_N - 1) / TILE_N;
     const long long tiles = (long long)m_blocks * n_blocks;
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    return launch_gemm(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tm_a, tm_b, tm_b2, tm_c, act_scale,
+    return launch_gemm(kern, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tm_a, tm_b, tm_b2, tm_c, act_scale,
                        w_scale, bias, w_scale2, bias2, out, M, N, K, a_rows, status) == cudaSuccess
                ? kOk
                : kLaunchFailed;
@@ -522,6 +546,12 @@ int dense_dispatch(const int8_t* A, const int8_t* B, const float* act_scale, con
         }
         bn = best;
     }
+    // One block of token rows in 64-column tiles: stages of two K atoms and a second producer thread (DenseCfg),
+    // four stages deep. N = 4096, K = 14336, 16-128 tokens: 31.4 -> 24.0-24.9 us; N = K = 4096: 12.0 -> 10.2 us.
+    // The wider tiles have room for three such stages only and gain nothing (80 columns, N = 11008, K = 4096:
+    // 13.4 -> 13.4 us at 16 tokens, 13.8 -> 14.2 us at 128). Knob 10 = 1 keeps the one-atom form for comparison.
+    if (M <= BLOCK_M && bn == 64 && tuning_knob(kKnobDenseOneAtom) == 0)
+        return launch_dense<64, EPI, 2>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
     switch (bn) {
     case 256: return launch_dense<256, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);
     case 128: return launch_dense<128, EPI>(A, B, act_scale, w_scale, bias, out, M, K, N, stream);

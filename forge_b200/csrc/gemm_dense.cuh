@@ -48,6 +48,7 @@ enum TuningKnob : int {
     kKnobGemvMaxTokens = 6,    // 1-4 token sparse kernel: largest M it takes (default 2)
     kKnobDenseBand = 7,        // dense CTA-pair kernel: 256-row blocks per raster band
     kKnobGemvDenseMaxTokens = 9,  // dense streaming kernel: largest M it takes (default 2, at most 16; negative: never)
+    kKnobDenseOneAtom = 10,    // dense single-CTA kernel: 1 = one K atom per stage also for M <= 128 (measurement)
     kKnobDependentLaunch = 8,  // CTA-pair kernels as programmatic dependents: 0 = where requested, 1 = always, 2 = never
 };
 int tuning_knob(int key);
