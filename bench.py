@@ -105,13 +105,15 @@ class ClockSampler(threading.Thread):
             get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
                 nv.nvmlDeviceGetCurrentClocksThrottleReasons
             while not self._halt.is_set():
-                if self.active.is_set():
-                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                    r = get_reasons(h)
-                    for bit, name in names.items():
-                        if r & bit:
-                            self.reasons.add(name)
-                time.sleep(0.002 if self.active.is_set() else 0.02)
+                # wakes up as soon as the timed region starts (a region of 20 steps lasts a few milliseconds)
+                if not self.active.wait(timeout=0.02):
+                    continue
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = get_reasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.0005)
         except Exception as e:  # clocks are evidence, not the product: report the failure, keep benchmarking
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
